@@ -251,7 +251,7 @@ void qie_engine_destroy(qie_engine* e);
  * differential attention, window attention beside an RG-LRU recurrence, Mamba-2; same loader) and "Qwen2ForCausalLM" /
  * "Qwen3ForCausalLM" (converted to the blob format in a temporary folder, HF semantics).  qie_model_families returns
  * the registered architecture names separated by commas; qie_engine_family the name of an engine's family
- * ("qwen" / "nogatar" / "fosavik"). */
+ * ("qwen" / "nogatar" / "fosavik" / "ditenex"). */
 int qie_engine_create_from_dir(const char* model_dir, const qie_engine_opts* opts, qie_engine** out);
 /* The same family over generated weights (measurement, tests): config_json is the text of a config.json. */
 int qie_engine_create_synthetic_json(const char* config_json, uint64_t seed, const qie_engine_opts* opts, qie_engine** out);

@@ -1,0 +1,45 @@
+// activations.cu -- elementwise activations of feed-forward layers on fp32 rows (ditenex.h): xIELU with its two learned
+// numbers, and the SiLU-gated product of a [gate | up] row.
+#include "ditenex.h"
+#include "launch.h"
+
+namespace qie {
+namespace {
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+__global__ void xielu_kernel(float* __restrict__ z, int ld, int cols, const bf16* __restrict__ pq) {
+  pdl_wait();
+  pdl_trigger();
+  const float ap = softplus_f(bf2f(pq[0])), an = 0.5f + softplus_f(bf2f(pq[1]));
+  float* row = z + (size_t)blockIdx.x * ld;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    const float v = row[i];
+    row[i] = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
+  }
+}
+
+__global__ void silu_glu_kernel(const float* gu, int ld, float* out, int ldo, int ff) {  // out may be gu (a thread reads its elements first)
+  pdl_wait();
+  pdl_trigger();
+  const float* row = gu + (size_t)blockIdx.x * ld;
+  float* o = out + (size_t)blockIdx.x * ldo;
+  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+    const float g = row[i];
+    o[i] = g / (1.0f + expf(-g)) * row[ff + i];
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_xielu(float* z, int ld, int cols, const bf16* pq, int n, cudaStream_t st) {
+  if (n <= 0 || cols <= 0) return cudaSuccess;
+  return launch_k(xielu_kernel, dim3(n), dim3(256), 0, st, z, ld, cols, pq);
+}
+
+cudaError_t launch_silu_glu(const float* gu, int ld, float* out, int ldo, int ff, int n, cudaStream_t st) {
+  if (n <= 0 || ff <= 0) return cudaSuccess;
+  return launch_k(silu_glu_kernel, dim3(n), dim3(256), 0, st, gu, ld, out, ldo, ff);
+}
+
+}  // namespace qie

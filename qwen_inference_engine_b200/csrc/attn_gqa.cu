@@ -39,19 +39,27 @@ __global__ void __launch_bounds__(128) kv_store_rows_kernel(const KvStoreArgs a)
   if (a.c.pool && a.k) {
     char* row = const_cast<char*>(kv_row_ptr(a.c, a.block_table, a.max_pages, a.slot[r], a.pos[r]));
     const float* k = a.k + (size_t)r * a.ldk;
+    auto key = [&](int i) { return a.k_bias ? k[i] + bf2f(a.k_bias[i]) : k[i]; };
     if (a.k_norm) {
       const int d = a.norm_dim;
       for (int g = warp; g < a.c.kw / d; g += nw) {
         float s = 0.f;
-        for (int i = lane; i < d; i += 32) s = fmaf(k[g * d + i], k[g * d + i], s);
+        for (int i = lane; i < d; i += 32) s = fmaf(key(g * d + i), key(g * d + i), s);
         const float rstd = 1.0f / sqrtf(warp_sum(s) / (float)d + a.eps);
-        for (int i = lane; i < d; i += 32) store_elt(a.c, row, g * d + i, k[g * d + i] * rstd * bf2f(a.k_norm[i]));
+        for (int i = lane; i < d; i += 32) store_elt(a.c, row, g * d + i, key(g * d + i) * rstd * bf2f(a.k_norm[i]));
       }
     } else {
-      for (int i = threadIdx.x; i < a.c.kw; i += blockDim.x) store_elt(a.c, row, i, k[i]);
+      for (int i = threadIdx.x; i < a.c.kw; i += blockDim.x) store_elt(a.c, row, i, key(i));
     }
     const float* v = a.v + (size_t)r * a.ldv;
-    for (int i = threadIdx.x; i < a.c.vw; i += blockDim.x) store_elt(a.c, row, a.c.kw + i, v[i]);
+    const bool blend = a.v_lam && a.v_other;
+    const float lam = blend ? bf2f(*a.v_lam) : 0.f;
+    for (int i = threadIdx.x; i < a.c.vw; i += blockDim.x) {
+      float x = a.v_bias ? v[i] + bf2f(a.v_bias[i]) : v[i];
+      if (blend) x = (1.0f - lam) * x + lam * a.v_other[(size_t)r * a.ld_vo + i];
+      if (a.v_keep) a.v_keep[(size_t)r * a.ld_vk + i] = x;
+      store_elt(a.c, row, a.c.kw + i, x);
+    }
   }
   if (a.q && a.q_norm) {
     float* q = a.q + (size_t)r * a.ldq;
@@ -70,6 +78,7 @@ __global__ void __launch_bounds__(128) kv_store_rows_kernel(const KvStoreArgs a)
 __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnArgs a, int hpc, int chunks, int n_splits) {
   extern __shared__ float sm[];
   __shared__ const char* rowp[ATK];
+  __shared__ int dist[ATK];  // pos - j of the tile's keys
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x, split = blockIdx.z;
@@ -104,7 +113,7 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
 #pragma unroll
   for (int i = 0; i < AMAXACC; ++i) acc[i] = 0.f;
   const int nacc = QV * vd;
-  const size_t koff = (size_t)g * kd, voff = (size_t)a.c.kw + (size_t)g * vd;
+  const size_t koff = a.shared_keys ? 0 : (size_t)g * kd, voff = (size_t)a.c.kw + (size_t)g * vd;
   const bool vec8 = a.c.elt_bytes == 2 && (a.c.page_elems % 8 == 0) && (a.c.layer_off % 8 == 0) && ((a.c.kw + a.c.vw) % 8 == 0) && (kd % 8 == 0) &&
                     (vd % 8 == 0) && (a.c.kw % 8 == 0);
   for (int t0 = i0; t0 < i1; t0 += ATK) {
@@ -114,6 +123,7 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
       const int i = t0 + tid;
       const int j = i < nfirst ? i : lo + (i - nfirst);
       rowp[tid] = kv_row_ptr(a.c, a.block_table, a.max_pages, slot, j);
+      dist[tid] = pos - j;
     }
     __syncthreads();
     if (a.c.elt_bytes == 4) {
@@ -159,6 +169,7 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
         const float* kp = Kt + key * (kd + 1) + (qv % maps) * dim;
         s = 0.f;
         for (int c = 0; c < dim; ++c) s = fmaf(qp[c], kp[c], s);
+        if (a.slopes) s -= a.slopes[h0 + qv / maps] * (float)dist[key];
       }
       sc[i] = s;
     }
@@ -264,6 +275,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
   const int pos0 = a.pos[row0];                       // rows of a segment are consecutive positions
   const int pmax = pos0 + nrows - 1;
   const int lo_min = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  const float slope = a.slopes ? a.slopes[h] : 0.f;
   const int qr = lane >> 2, qc = (lane & 3) * 2;      // this thread's rows qr, qr + 8 and column pair of every 8-block
   const int wrow = warp * 16;
   const bool rv0 = wrow + qr < nrows, rv1 = wrow + qr + 8 < nrows;
@@ -308,7 +320,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
         const int key = i / (DP / 8), c = (i % (DP / 8)) * 8;
         bf16* dst = &Ks[buf][key][c];
         if (jb + key <= pmax && c < dim) {
-          const bf16* src = reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, jb + key)) + (size_t)g * kd + mp * dim + c;
+          const bf16* src = reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, jb + key)) + (a.shared_keys ? 0 : (size_t)g * kd) + mp * dim + c;
           if (vec) cp_async16(smem_u32(dst), src);
           else
             for (int e = 0; e < 8; ++e) dst[e] = c + e < dim ? src[e] : f2bf(0.f);
@@ -363,7 +375,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
           const int j = j0 + nb * 8 + qc + (e & 1);
           const int i = (e >> 1) ? i1 : i0;
           const bool ok = j <= i && (a.window <= 0 || i - j < a.window || j < a.keep_first);
-          s[nb][e] = ok ? s[nb][e] * a.scale : -INFINITY;  // the scale meets the fp32 score, not the bf16 operand
+          s[nb][e] = ok ? s[nb][e] * a.scale - slope * (float)(i - j) : -INFINITY;  // the scale meets the fp32 score, not the bf16 operand
           if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
           else mx0 = fmaxf(mx0, s[nb][e]);
         }
@@ -442,6 +454,10 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
         if (c + e >= vd) continue;
         float v0 = o[vb][e] * f0, v1 = o[vb][2 + e] * f1;
         if (last && a.finish == 1) v0 *= g0, v1 *= g1;
+        if (last && a.finish == 3) {
+          if (rv0) v0 *= 1.0f / (1.0f + expf(-a.gate[(size_t)(row0 + wrow + qr) * a.ldg + (size_t)h * vd + c + e]));
+          if (rv1) v1 *= 1.0f / (1.0f + expf(-a.gate[(size_t)(row0 + wrow + qr + 8) * a.ldg + (size_t)h * vd + c + e]));
+        }
         if (last && a.finish == 2) {  // the first map's result was parked in the output rows by this thread
           v0 = (rv0 ? out0[c + e] : 0.f) - a.lam * v0;
           v1 = (rv1 ? out1[c + e] : 0.f) - a.lam * v1;
@@ -528,6 +544,7 @@ __global__ void __launch_bounds__(128) gqa_finish_kernel(const GqaAttnArgs a, in
     float v = am[0];
     if (a.finish == 1) v *= gate;
     else if (a.finish == 2) v = am[0] - a.lam * am[1];
+    else if (a.finish == 3) v *= 1.0f / (1.0f + expf(-a.gate[(size_t)r * a.ldg + (size_t)h * vd + c]));
     o[c] = v;
     sq = fmaf(v, v, sq);
   }
@@ -544,7 +561,41 @@ __global__ void __launch_bounds__(128) gqa_finish_kernel(const GqaAttnArgs a, in
   for (int c = threadIdx.x; c < vd; c += blockDim.x) out[c] = o[c] * rstd;
 }
 
+// one CTA per row; thread = (head h, kv head c, element e) of the mixed queries
+__global__ void __launch_bounds__(256) talk_queries_kernel(const float* __restrict__ q, int ldq, const bf16* __restrict__ q_bias,
+                                                           const bf16* __restrict__ talk, float* __restrict__ qt, int ldqt, int heads, int kv_heads,
+                                                           int dim) {
+  extern __shared__ float tq[];  // q row (bias added) [heads * dim] | talk [heads * heads]
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, hpg = heads / kv_heads, kd = kv_heads * dim;
+  float* qs = tq;
+  float* tk = tq + heads * dim;
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) qs[i] = q[(size_t)r * ldq + i] + (q_bias ? bf2f(q_bias[i]) : 0.f);
+  for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) tk[i] = bf2f(talk[i]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < heads * kd; i += blockDim.x) {
+    const int h = i / kd, c = (i - h * kd) / dim, e = i - h * kd - c * dim;
+    float v = 0.f;
+    for (int g = c * hpg; g < (c + 1) * hpg; ++g) v = fmaf(tk[h * heads + g], qs[g * dim + e], v);
+    qt[(size_t)r * ldqt + i] = v;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_talk_queries(const float* q, int ldq, const bf16* q_bias, const bf16* talk, float* qt, int ldqt, int heads, int kv_heads, int dim,
+                                int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) return cudaErrorInvalidValue;
+  const size_t smem = ((size_t)heads * dim + (size_t)heads * heads) * sizeof(float);
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    cudaError_t r = cudaFuncSetAttribute(talk_queries_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(talk_queries_kernel, dim3(n), dim3(256), smem, st, q, ldq, q_bias, talk, qt, ldqt, heads, kv_heads, dim);
+}
 
 cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;
@@ -555,6 +606,8 @@ cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st) {
 cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_launches) {
   if (n_launches) *n_launches = 0;
   if (a.n <= 0) return cudaSuccess;
+  if (a.shared_keys && (a.maps != 1 || a.dim != a.c.kw)) return cudaErrorInvalidValue;
+  if (a.finish == 3 && !a.gate) return cudaErrorInvalidValue;
   // prompt portions over a bf16 cache: the tensor-core kernel (one launch, no workspace); QIE_ATTN_MMA=0 keeps the per-row kernel (A/B)
   static const bool mma_on = [] { const char* v = getenv("QIE_ATTN_MMA"); return !(v && v[0] == '0'); }();
   if (mma_on && a.seg_start && a.c.elt_bytes == 2 && a.n >= 64 && a.dim <= 128 && a.vdim <= 128 && a.maps <= 2 && a.heads % a.kv_heads == 0 &&

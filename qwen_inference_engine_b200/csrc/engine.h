@@ -13,6 +13,7 @@
 
 #include "checkpoint.h"
 #include "kernels.h"
+#include "ditenex.h"
 #include "fosavik.h"
 #include "nogatar.h"
 #include "tp_nccl.h"
@@ -43,11 +44,12 @@ struct CaptureBuf {
 }  // namespace qie
 
 struct qie_engine {
-  // model family: Qwen (the members below named after its operators) unless `fam` is set (nogatar.h, fosavik.h); sequences, pages,
+  // model family: Qwen (the members below named after its operators) unless `fam` is set (nogatar.h, fosavik.h, ditenex.h); sequences, pages,
   // block tables, row metadata, sampling and graphs are shared by the families
-  qie::RowFamily* fam = nullptr;  // the family's interface (family.h); ng / fv below are the same object, typed
+  qie::RowFamily* fam = nullptr;  // the family's interface (family.h); ng / fv / dx below are the same object, typed
   qie::NgModel* ng = nullptr;
   qie::FvModel* fv = nullptr;
+  qie::DxModel* dx = nullptr;
   qie_config cfg{};
   qie_engine_opts opts{};
   int num_sms = 0;

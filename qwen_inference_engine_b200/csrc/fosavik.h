@@ -62,6 +62,8 @@ struct KvRowCache {
 };
 // per row: keys k[r, 0:kw] (optionally unit-RMS normed per `norm_dim` consecutive elements, times k_norm) and values
 // v[r, 0:vw] -> cache row (slot, pos).  Rider: the row's queries q[r, 0:q_heads*norm_dim] normed in place with q_norm.
+// Optional: biases added to keys and values first; values blended with another layer's values of the same rows,
+// v = (1 - lam) v + lam v_other (lam one bf16 number on the device); the stored values also kept as fp32 rows (v_keep).
 struct KvStoreArgs {
   KvRowCache c;
   const float* k = nullptr;
@@ -74,6 +76,13 @@ struct KvStoreArgs {
   float* q = nullptr;
   int ldq = 0, q_heads = 0;
   const bf16* q_norm = nullptr;
+  const bf16* k_bias = nullptr;  // [kw]
+  const bf16* v_bias = nullptr;  // [vw]
+  const bf16* v_lam = nullptr;
+  const float* v_other = nullptr;
+  int ld_vo = 0;
+  float* v_keep = nullptr;
+  int ld_vk = 0;
   const int *pos = nullptr, *slot = nullptr, *block_table = nullptr;
   int max_pages = 0, n = 0;
 };
@@ -81,7 +90,12 @@ cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st);
 // out[r, h, :] over the keys j of row r's sequence with j <= pos and (window <= 0 or pos - j < window or j < keep_first).
 // `maps` score maps per head (queries [h][map][dim], keys [g][map][dim]) share the values [g][vdim]; head h reads kv
 // head h / (heads / kv_heads).  unit_sink adds 1 to every softmax denominator (as if one more key with a zero score and nothing to contribute took part).
-// finish 0: out = a_1;  1: out = a_1 * sigmoid(gate[r, h]);  2 (maps == 2): o = a_1 - lam * a_2, out = o / sqrt(mean(o^2) + eps) * post.
+// finish 0: out = a_1;  1: out = a_1 * sigmoid(gate[r, h]);  2 (maps == 2): o = a_1 - lam * a_2, out = o / sqrt(mean(o^2) + eps) * post;
+// 3: out[r, h, c] = a_1[c] * sigmoid(gate[r, h * vdim + c]) (a gate per element).
+// slopes (optional, [heads] fp32): slopes[h] * (pos - j) is taken off the scaled score of key j (a linear distance penalty).
+// shared_keys: every head scores against the WHOLE key part of the cached row (dim = kw / maps elements: the keys of all
+// kv heads side by side) while its values stay those of kv head h / (heads / kv_heads); the queries are then
+// [h][map][kw / maps] (launch_talk_queries builds them).
 // The keys of a row may be split over CTAs; partial (max, sum, acc) go through ws and a second kernel finishes.
 struct GqaAttnArgs {
   KvRowCache c;
@@ -95,6 +109,8 @@ struct GqaAttnArgs {
   int finish = 0;
   const float* gate = nullptr;
   int ldg = 0;
+  const float* slopes = nullptr;
+  int shared_keys = 0;
   float lam = 0.f, post = 1.f, eps = 0.f;
   const int *pos = nullptr, *slot = nullptr, *block_table = nullptr;
   int max_pages = 0, n = 0, max_keys = 0;
@@ -110,6 +126,12 @@ struct GqaAttnArgs {
 // floats of workspace that n rows need with one split
 inline size_t gqa_ws_floats(int n, int heads, int maps, int vdim) { return (size_t)n * heads * maps * (vdim + 2); }
 cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_launches = nullptr);
+// Mixing the heads' scores before the softmax, score'_h = sum_g talk[h, g] score_g, is linear in the queries: with
+// qt[r, h, c * dim + e] = sum over the heads g of kv head c of talk[h, g] * (q[r, g, e] + q_bias[g * dim + e])
+// head h's mixed score against key j is qt[r, h, :] . [keys of all kv heads of j] (shared_keys above), and distance
+// slopes mix the same way (slopes'_h = sum_g talk[h, g] slopes_g, a constant of the layer).  q_bias may be null.
+cudaError_t launch_talk_queries(const float* q, int ldq, const bf16* q_bias, const bf16* talk, float* qt, int ldqt, int heads, int kv_heads, int dim,
+                                int n, cudaStream_t st);
 
 // ---------------------------------------------------------------- short convolution and recurrences (recurrent.cu)
 // Causal per-channel convolution over the rows of each segment: out[t, c] = act(b[c] + sum_i w[c, i] * in(t - (taps-1-i), c)),

@@ -22,6 +22,7 @@ struct Row {
 const Row kRegistry[] = {
     {"Nogatar", FAMILY_NOGATAR},
     {"Fosavik", FAMILY_FOSAVIK},
+    {"Ditenex", FAMILY_DITENEX},
     {"Qwen2ForCausalLM", FAMILY_QWEN},
     {"Qwen3ForCausalLM", FAMILY_QWEN},
 };

@@ -1,0 +1,130 @@
+// rmsnorm_f32.cu -- RMS norms of a model whose sublayers sit between two norms (ditenex.h): the output norm folded
+// into the residual add together with the next sublayer's input norm, and the input norm of a mixer that reads a blend
+// of each row with the row before it (token shift) with one carried row per sequence slot.  All fp32, one CTA per row,
+// every reduction in a fixed order per row, so a row's result does not depend on the rows it shares a launch with.
+#include "ditenex.h"
+#include "launch.h"
+
+namespace qie {
+namespace {
+
+__device__ __forceinline__ float block_sum_r(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();  // red may still be read from the previous call
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+__global__ void __launch_bounds__(256) rms_step_kernel(const RmsStep a) {
+  extern __shared__ float row[];  // [width]
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, W = a.width;
+  const bool add = a.y || a.mix.ye;
+  const int src = a.gather ? a.gather[r] : r;  // the add half is never combined with a gather
+  float* xr = a.x + (size_t)src * W;
+  float sq = 0.f;
+  if (add) {
+    float s = 0.f;
+    if (a.y) {
+      const float* y = a.y + (size_t)r * W;
+      for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = y[i];
+        row[i] = v;
+        s = fmaf(v, v, s);
+      }
+    } else {  // the chosen experts' outputs of this row, weighted, plus the shared expert (gated only when mix.z is given)
+      const MoeMix& m = a.mix;
+      const float sg = m.ys ? (m.z ? 1.0f / (1.0f + expf(-m.z[(size_t)r * m.ldz + m.gate_col])) : 1.0f) : 0.f;
+      for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = 0.f;
+        for (int k = 0; k < m.top; ++k) v = fmaf(m.top_w[(size_t)r * m.top + k], m.ye[(size_t)m.slot_of[(size_t)r * m.top + k] * W + i], v);
+        if (m.ys) v = fmaf(sg, m.ys[(size_t)r * W + i], v);
+        row[i] = v;
+        s = fmaf(v, v, s);
+      }
+    }
+    const float rstd = 1.0f / sqrtf(block_sum_r(s, red) / (float)W + a.eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = xr[i] + a.mult * (row[i] * rstd * bf2f(a.w_out[i]));
+      xr[i] = v;
+      row[i] = v;
+      sq = fmaf(v, v, sq);
+    }
+  } else if (a.h) {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = xr[i];
+      row[i] = v;
+      sq = fmaf(v, v, sq);
+    }
+  }
+  if (!a.h) return;
+  const float rstd = 1.0f / sqrtf(block_sum_r(sq, red) / (float)W + a.eps);
+  float* h = a.h + (size_t)r * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) h[i] = row[i] * rstd * bf2f(a.w_in[i]);
+}
+
+// one CTA per row.  The CTA of a segment's first row also moves the segment's last normed row into the carried row:
+// each thread reads the old carried elements it needs before it overwrites exactly those, and no other CTA touches them.
+__global__ void __launch_bounds__(256) rms_shift_kernel(const RmsShiftArgs a) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, W = a.width;
+  // the segment of this row: the last s with seg_start[s] <= r
+  int lo = 0, hi = a.n_seg - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (a.seg_start[mid] <= r) lo = mid;
+    else hi = mid - 1;
+  }
+  const int first = a.seg_start[lo], last = a.seg_start[lo + 1] - 1;
+  const bool head = r == first;
+  const float* xr = a.x + (size_t)r * W;
+  const float* xp = head ? a.x + (size_t)last * W : xr - W;  // the other row this CTA norms: the one before, or (first row) the segment's last
+  float s0 = 0.f, s1 = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = xr[i], u = xp[i];
+    s0 = fmaf(v, v, s0);
+    s1 = fmaf(u, u, s1);
+  }
+  const float r0 = 1.0f / sqrtf(block_sum_r(s0, red) / (float)W + a.eps);
+  const float r1 = 1.0f / sqrtf(block_sum_r(s1, red) / (float)W + a.eps);
+  float* carry = a.carry + (size_t)a.seg_slot[lo] * a.slot_stride;
+  float* out = a.out + (size_t)r * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float w = bf2f(a.w[i]);
+    const float h = xr[i] * r0 * w, o = xp[i] * r1 * w;
+    const float before = head ? carry[i] : o;
+    out[i] = h + (before - h) * bf2f(a.mu[i]);
+    if (head) carry[i] = o;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_rms_step(const RmsStep& a, cudaStream_t st) {
+  if (a.n <= 0) return cudaSuccess;
+  const bool add = a.y || a.mix.ye;
+  if ((add && (!a.w_out || a.gather)) || (a.h && !a.w_in) || (!add && !a.h)) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)a.width * sizeof(float);
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    cudaError_t r = cudaFuncSetAttribute(rms_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(rms_step_kernel, dim3(a.n), dim3(256), smem, st, a);
+}
+
+cudaError_t launch_rms_shift(const RmsShiftArgs& a, cudaStream_t st) {
+  if (a.n <= 0) return cudaSuccess;
+  if (a.n_seg <= 0 || !a.seg_start || !a.seg_slot || !a.carry) return cudaErrorInvalidValue;
+  return launch_k(rms_shift_kernel, dim3(a.n), dim3(256), 0, st, a);
+}
+
+}  // namespace qie
