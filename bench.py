@@ -459,6 +459,32 @@ def fosavik_macs_per_token(cfg):
     return mac
 
 
+def ditenex_config(z, vocab=32000):
+    """four layers of window attention with head-mixed scores (two kv heads of 64 side by side in the key row, values of 128,
+    blended with the first layer's), dense xIELU feed-forwards (no gate matrix: 1.5 x the gated width for equal work) and
+    group-limited mixtures of experts with a shared expert, alternating"""
+    W = z["width"]
+    mx = {"dim": 64, "heads": W // 128, "kv_heads": 2, "mask": {"size": z["window"]}, "scale": 0.125, "v_mix": True, "vdim": 128}
+    dense = {"ff": 3 * (z["top"] * z["ff"] + z["sff"]) // 2, "kind": "dense"}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "shared": {"ff": z["sff"]},
+           "router": {"experts": z["experts"], "groups": {"count": 4, "keep": 2}, "scale": 1.5, "top": z["top"]}}
+    layers = [{"type": "attention", "mixer": mx, "mlp": m} for m in (dense, moe, dense, moe)]
+    return {"architecture": "Ditenex", "layers": layers, "max_positions": 8192, "norm": {"eps": 1e-6}, "residual_mult": 0.3, "vocab": vocab, "width": W}
+
+
+def ditenex_macs_per_token(cfg):
+    """multiply-adds of the projections of one token (attention scores not counted)"""
+    W, mac = cfg["width"], 0
+    for ly in cfg["layers"]:
+        mx, mlp = ly["mixer"], ly.get("mlp")
+        mac += W * (mx["heads"] * mx["dim"] + mx["kv_heads"] * (mx["dim"] + mx["vdim"]) + mx["heads"] * mx["vdim"]) + mx["heads"] * mx["vdim"] * W
+        if mlp and mlp["kind"] == "dense":
+            mac += 2 * W * mlp["ff"]
+        elif mlp:
+            mac += 3 * W * (mlp["router"]["top"] * mlp["expert"]["ff"] + (mlp.get("shared") or {"ff": 0})["ff"]) + W * mlp["router"]["experts"]
+    return mac
+
+
 def run_family_compare(args):
     import numpy as np
     import torch
@@ -544,6 +570,11 @@ def run_family_compare(args):
             fv_cfg = json.dumps(fv)
             rec["fosavik"] = measure(lambda rows, seqs: q.Engine(config_json=fv_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
                                                                  max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False)
+        if args.family == "ditenex":
+            dx = ditenex_config(z, vocab)
+            dx_cfg = json.dumps(dx)
+            rec["ditenex"] = measure(lambda rows, seqs: q.Engine(config_json=dx_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
+                                                                 max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False)
         rec.update({"nogatar": measure(lambda rows, seqs: q.Engine(config_json=ng_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
                                                               max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False),
                "qwen_fast": measure(lambda rows, seqs: q.Engine(synthetic=qcfg, seed=7, numerics="fast", page_size=16, max_pages=pages, max_seqs=seqs,
@@ -561,6 +592,9 @@ def run_family_compare(args):
         if args.family == "fosavik":
             rec["macs_per_token"]["fosavik"] = fosavik_macs_per_token(fv)
             fams.append(("fosavik", rec["macs_per_token"]["fosavik"]))
+        if args.family == "ditenex":
+            rec["macs_per_token"]["ditenex"] = ditenex_macs_per_token(dx)
+            fams.append(("ditenex", rec["macs_per_token"]["ditenex"]))
         for fam, mac in fams:
             r = rec[fam]
             r["prefill_tflops"] = 2 * mac * T / (r["prefill_ms"] / 1e3) / 1e12
@@ -587,8 +621,8 @@ def main():
     ap.add_argument("--family-compare", action="store_true",
                     help="side measurement (not the contract line): prefill / decode throughput of the Nogatar family beside the "
                          "Qwen family at equal size, with per-kernel-class device times")
-    ap.add_argument("--family", default="nogatar", choices=["nogatar", "fosavik"],
-                    help="with --family-compare: which fp32-stream family is measured beside the Qwen family (fosavik also runs nogatar)")
+    ap.add_argument("--family", default="nogatar", choices=["nogatar", "fosavik", "ditenex"],
+                    help="with --family-compare: which fp32-stream family is measured beside the Qwen family (fosavik and ditenex also run nogatar)")
     ap.add_argument("--family-size", default="", help="one of " + ", ".join(FAMILY_SIZES) + " (default: all)")
     ap.add_argument("--family-tokens", type=int, default=2048)
     ap.add_argument("--family-ctx", type=int, default=1024)
