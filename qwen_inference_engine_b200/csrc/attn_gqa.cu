@@ -245,19 +245,22 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
   KTile* Ks = reinterpret_cast<KTile*>(pt_smem);
   VTile* Vs = reinterpret_cast<VTile*>(pt_smem + 2 * sizeof(KTile));
   __shared__ int tile_info[5];  // segment's first row, its length, slot, the CTA's two tiles (-1: none)
+  __shared__ const bf16* krow[2][PT_KEYS];  // cache rows of the keys of a stage (null: beyond the tile's last position)
   pdl_wait();
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     // a CTA takes tile p and tile nt-1-p of a segment: under a causal mask the late tiles see many key blocks and the early
     // ones few, so every CTA gets about the same number
+    // (under a sliding window every tile sees about the same number: one tile per CTA, twice the CTAs)
+    const bool pair = a.window <= 0;
     int left = blockIdx.x, found = 0;
     for (int s = 0; s < n_seg && !found; ++s) {
-      const int r0 = seg_start[s], len = seg_start[s + 1] - r0, nt = (len + PT_ROWS - 1) / PT_ROWS, np = (nt + 1) / 2;
+      const int r0 = seg_start[s], len = seg_start[s + 1] - r0, nt = (len + PT_ROWS - 1) / PT_ROWS, np = pair ? (nt + 1) / 2 : nt;
       if (left < np) {
         tile_info[0] = r0, tile_info[1] = len, tile_info[2] = seg_slot[s];
-        tile_info[3] = nt - 1 - left;
-        tile_info[4] = left != nt - 1 - left ? left : -1;
+        tile_info[3] = pair ? nt - 1 - left : left;
+        tile_info[4] = pair && left != nt - 1 - left ? left : -1;
         found = 1;
       }
       left -= np;
@@ -316,11 +319,15 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
     };
     // a key block -> stage `buf` (cp.async when every piece of a cache row starts on a 16-byte boundary); one commit group
     auto stage = [&](int jb, int buf) {
+      if (tid < PT_KEYS)  // one page lookup per key, not per 16-byte piece
+        krow[buf][tid] = jb + tid <= pmax ? reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, jb + tid)) : nullptr;
+      __syncthreads();
       for (int i = tid; i < PT_KEYS * (DP / 8); i += 128) {
         const int key = i / (DP / 8), c = (i % (DP / 8)) * 8;
         bf16* dst = &Ks[buf][key][c];
-        if (jb + key <= pmax && c < dim) {
-          const bf16* src = reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, jb + key)) + (a.shared_keys ? 0 : (size_t)g * kd) + mp * dim + c;
+        const bf16* row = krow[buf][key];
+        if (row && c < dim) {
+          const bf16* src = row + (a.shared_keys ? 0 : (size_t)g * kd) + mp * dim + c;
           if (vec) cp_async16(smem_u32(dst), src);
           else
             for (int e = 0; e < 8; ++e) dst[e] = c + e < dim ? src[e] : f2bf(0.f);
@@ -331,8 +338,9 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
       for (int i = tid; i < PT_KEYS * (VP / 8); i += 128) {
         const int key = i / (VP / 8), c = (i % (VP / 8)) * 8;
         bf16* dst = &Vs[buf][key][c];
-        if (jb + key <= pmax && c < vd) {
-          const bf16* src = reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, jb + key)) + a.c.kw + (size_t)g * vd + c;
+        const bf16* row = krow[buf][key];
+        if (row && c < vd) {
+          const bf16* src = row + a.c.kw + (size_t)g * vd + c;
           if (vec) cp_async16(smem_u32(dst), src);
           else
             for (int e = 0; e < 8; ++e) dst[e] = c + e < vd ? src[e] : f2bf(0.f);
@@ -368,33 +376,48 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
       }
       // mask, running maximum
       float mx0 = -INFINITY, mx1 = -INFINITY;
+      // a block that every row of the warp sees whole (below the diagonal, inside the window) needs no mask
+      const bool whole = j0 + PT_KEYS - 1 <= pos0 + wrow && (a.window <= 0 || pos0 + wrow + 15 - j0 < a.window);
+      if (whole) {
+        const float d0 = -slope * (float)(i0 - j0 - qc), d1 = -slope * (float)(i1 - j0 - qc);  // minus slope times the distance to the thread's first column
 #pragma unroll
-      for (int nb = 0; nb < PT_KEYS / 8; ++nb)
+        for (int nb = 0; nb < PT_KEYS / 8; ++nb)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = j0 + nb * 8 + qc + (e & 1);
-          const int i = (e >> 1) ? i1 : i0;
-          const bool ok = j <= i && (a.window <= 0 || i - j < a.window || j < a.keep_first);
-          s[nb][e] = ok ? s[nb][e] * a.scale - slope * (float)(i - j) : -INFINITY;  // the scale meets the fp32 score, not the bf16 operand
-          if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
-          else mx0 = fmaxf(mx0, s[nb][e]);
-        }
+          for (int e = 0; e < 4; ++e) {
+            s[nb][e] = fmaf(s[nb][e], a.scale, fmaf(slope, (float)(nb * 8 + (e & 1)), (e >> 1) ? d1 : d0));
+            if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
+            else mx0 = fmaxf(mx0, s[nb][e]);
+          }
+      } else {
+#pragma unroll
+        for (int nb = 0; nb < PT_KEYS / 8; ++nb)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = j0 + nb * 8 + qc + (e & 1);
+            const int i = (e >> 1) ? i1 : i0;
+            const bool ok = j <= i && (a.window <= 0 || i - j < a.window || j < a.keep_first);
+            s[nb][e] = ok ? s[nb][e] * a.scale - slope * (float)(i - j) : -INFINITY;  // the scale meets the fp32 score, not the bf16 operand
+            if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
+            else mx0 = fmaxf(mx0, s[nb][e]);
+          }
+      }
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-      const float c0 = mn0 > -INFINITY ? expf(m0 - mn0) : 1.f, c1 = mn1 > -INFINITY ? expf(m1 - mn1) : 1.f;
+      // the weights become bf16 operands below: the fast exponential's error is far under their rounding
+      const float c0 = mn0 > -INFINITY ? __expf(m0 - mn0) : 1.f, c1 = mn1 > -INFINITY ? __expf(m1 - mn1) : 1.f;
       m0 = mn0, m1 = mn1;
       l0 *= c0, l1 *= c1;
 #pragma unroll
       for (int i = 0; i < VP / 8; ++i) o[i][0] *= c0, o[i][1] *= c0, o[i][2] *= c1, o[i][3] *= c1;
 #pragma unroll
       for (int nb = 0; nb < PT_KEYS / 8; ++nb) {
-        s[nb][0] = mn0 > -INFINITY ? expf(s[nb][0] - mn0) : 0.f;
-        s[nb][1] = mn0 > -INFINITY ? expf(s[nb][1] - mn0) : 0.f;
-        s[nb][2] = mn1 > -INFINITY ? expf(s[nb][2] - mn1) : 0.f;
-        s[nb][3] = mn1 > -INFINITY ? expf(s[nb][3] - mn1) : 0.f;
+        s[nb][0] = mn0 > -INFINITY ? __expf(s[nb][0] - mn0) : 0.f;
+        s[nb][1] = mn0 > -INFINITY ? __expf(s[nb][1] - mn0) : 0.f;
+        s[nb][2] = mn1 > -INFINITY ? __expf(s[nb][2] - mn1) : 0.f;
+        s[nb][3] = mn1 > -INFINITY ? __expf(s[nb][3] - mn1) : 0.f;
         l0 += s[nb][0] + s[nb][1];
         l1 += s[nb][2] + s[nb][3];
       }
@@ -492,7 +515,8 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
 
 template <int DP, int VP>
 cudaError_t launch_prefill_mma_dv(const GqaAttnArgs& a, const int* seg_start, const int* seg_slot, int n_seg, cudaStream_t st) {
-  const dim3 grid((a.n + 2 * PT_ROWS - 1) / (2 * PT_ROWS) + n_seg, a.heads), block(128);  // upper bound of the tile pairs
+  const int per_cta = a.window <= 0 ? 2 * PT_ROWS : PT_ROWS;
+  const dim3 grid((a.n + per_cta - 1) / per_cta + n_seg, a.heads), block(128);  // upper bound of the tiles / tile pairs
   const size_t smem = (size_t)2 * PT_KEYS * ((DP + 8) + (VP + 8)) * sizeof(bf16);
   if (smem > 48 * 1024) {
     cudaError_t r = cudaFuncSetAttribute(gqa_prefill_mma_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
