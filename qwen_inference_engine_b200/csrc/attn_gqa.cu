@@ -30,11 +30,29 @@ __device__ __forceinline__ void store_elt(const KvRowCache& c, char* row, int i,
   else reinterpret_cast<bf16*>(row)[i] = f2bf(v);
 }
 
+// the mixed queries of row r; thread = (head h, kv head c, element e).  smem: q row (bias added) [heads * dim] | talk [heads * heads]
+__device__ __forceinline__ void talk_queries_row(const TalkQueries& t, int r, float* smem) {
+  const int heads = t.heads, dim = t.dim, hpg = heads / t.kv_heads, kd = t.kv_heads * dim;
+  float* qs = smem;
+  float* tk = smem + heads * dim;
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) qs[i] = t.q[(size_t)r * t.ldq + i] + (t.q_bias ? bf2f(t.q_bias[i]) : 0.f);
+  for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) tk[i] = bf2f(t.talk[i]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < heads * kd; i += blockDim.x) {
+    const int h = i / kd, c = (i - h * kd) / dim, e = i - h * kd - c * dim;
+    float v = 0.f;
+    for (int g = c * hpg; g < (c + 1) * hpg; ++g) v = fmaf(tk[h * heads + g], qs[g * dim + e], v);
+    t.qt[(size_t)r * t.ldqt + i] = v;
+  }
+}
+
 // one CTA per row, one warp per normed group
 __global__ void __launch_bounds__(128) kv_store_rows_kernel(const KvStoreArgs a) {
+  extern __shared__ float tq_smem[];  // only with the query rider
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x;
+  if (a.tq.talk) talk_queries_row(a.tq, r, tq_smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   if (a.c.pool && a.k) {
     char* row = const_cast<char*>(kv_row_ptr(a.c, a.block_table, a.max_pages, a.slot[r], a.pos[r]));
@@ -585,46 +603,43 @@ __global__ void __launch_bounds__(128) gqa_finish_kernel(const GqaAttnArgs a, in
   for (int c = threadIdx.x; c < vd; c += blockDim.x) out[c] = o[c] * rstd;
 }
 
-// one CTA per row; thread = (head h, kv head c, element e) of the mixed queries
-__global__ void __launch_bounds__(256) talk_queries_kernel(const float* __restrict__ q, int ldq, const bf16* __restrict__ q_bias,
-                                                           const bf16* __restrict__ talk, float* __restrict__ qt, int ldqt, int heads, int kv_heads,
-                                                           int dim) {
-  extern __shared__ float tq[];  // q row (bias added) [heads * dim] | talk [heads * heads]
+__global__ void __launch_bounds__(256) talk_queries_kernel(const TalkQueries t) {
+  extern __shared__ float tq_smem[];
   pdl_wait();
   pdl_trigger();
-  const int r = blockIdx.x, hpg = heads / kv_heads, kd = kv_heads * dim;
-  float* qs = tq;
-  float* tk = tq + heads * dim;
-  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) qs[i] = q[(size_t)r * ldq + i] + (q_bias ? bf2f(q_bias[i]) : 0.f);
-  for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) tk[i] = bf2f(talk[i]);
-  __syncthreads();
-  for (int i = threadIdx.x; i < heads * kd; i += blockDim.x) {
-    const int h = i / kd, c = (i - h * kd) / dim, e = i - h * kd - c * dim;
-    float v = 0.f;
-    for (int g = c * hpg; g < (c + 1) * hpg; ++g) v = fmaf(tk[h * heads + g], qs[g * dim + e], v);
-    qt[(size_t)r * ldqt + i] = v;
-  }
+  talk_queries_row(t, blockIdx.x, tq_smem);
 }
 
 }  // namespace
 
-cudaError_t launch_talk_queries(const float* q, int ldq, const bf16* q_bias, const bf16* talk, float* qt, int ldqt, int heads, int kv_heads, int dim,
-                                int n, cudaStream_t st) {
+static size_t talk_smem(const TalkQueries& t) { return ((size_t)t.heads * t.dim + (size_t)t.heads * t.heads) * sizeof(float); }
+
+cudaError_t launch_talk_queries(const TalkQueries& t, int n, cudaStream_t st) {
   if (n <= 0) return cudaSuccess;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) return cudaErrorInvalidValue;
-  const size_t smem = ((size_t)heads * dim + (size_t)heads * heads) * sizeof(float);
+  if (!t.talk || t.heads <= 0 || t.kv_heads <= 0 || t.heads % t.kv_heads) return cudaErrorInvalidValue;
+  const size_t smem = talk_smem(t);
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     cudaError_t r = cudaFuncSetAttribute(talk_queries_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (r != cudaSuccess) return r;
   }
-  return launch_k(talk_queries_kernel, dim3(n), dim3(256), smem, st, q, ldq, q_bias, talk, qt, ldqt, heads, kv_heads, dim);
+  return launch_k(talk_queries_kernel, dim3(n), dim3(256), smem, st, t);
 }
 
 cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;
   if (a.k_norm && (a.norm_dim <= 0 || a.c.kw % a.norm_dim)) return cudaErrorInvalidValue;
-  return launch_k(kv_store_rows_kernel, dim3(a.n), dim3(128), 0, st, a);
+  size_t smem = 0;
+  if (a.tq.talk) {
+    if (a.tq.heads <= 0 || a.tq.kv_heads <= 0 || a.tq.heads % a.tq.kv_heads) return cudaErrorInvalidValue;
+    smem = talk_smem(a.tq);
+    if (smem > 48 * 1024) {
+      if (smem > 200 * 1024) return cudaErrorInvalidValue;
+      cudaError_t r = cudaFuncSetAttribute(kv_store_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (r != cudaSuccess) return r;
+    }
+  }
+  return launch_k(kv_store_rows_kernel, dim3(a.n), dim3(128), smem, st, a);
 }
 
 cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_launches) {

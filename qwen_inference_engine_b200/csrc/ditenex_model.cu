@@ -366,16 +366,18 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
     KvRowCache c;
     c.pool = m->kv_pool, c.elt_bytes = m->f32 ? 4 : 2, c.page_size = e->kv.page_size, c.page_elems = m->page_elems;
     c.layer_off = L.kv_off, c.kw = Nk, c.vw = Nv;
-    {  // keys and values (+ biases, values blended with the first blending layer's) -> cache rows
+    {  // keys and values (+ biases, values blended with the first blending layer's) -> cache rows; head-mixed queries
       KvStoreArgs ks;
       ks.c = c, ks.k = m->p0 + Nq, ks.ldk = Nin, ks.v = m->p0 + Nq + Nk, ks.ldv = Nin;
       ks.k_bias = L.k_b, ks.v_bias = L.v_b;
       if (L.v_first) ks.v_keep = m->vf, ks.ld_vk = Nv;
       else if (L.v_mix) ks.v_lam = L.vmix, ks.v_other = m->vf, ks.ld_vo = Nv;
+      // rider: the queries (+ bias) mixed over the heads, one vector per head against the whole key row
+      ks.tq.q = m->p0, ks.tq.ldq = Nin, ks.tq.q_bias = L.q_b, ks.tq.talk = L.talk, ks.tq.qt = m->p2, ks.tq.ldqt = H * Nk;
+      ks.tq.heads = H, ks.tq.kv_heads = G, ks.tq.dim = d;
       ks.pos = e->pos_d, ks.slot = e->slot_d, ks.block_table = e->block_table_d, ks.max_pages = e->max_pages_per_seq, ks.n = n;
       FAM_TRY(KK_KV_STORE, launch_kv_store_rows(ks, st));
     }
-    FAM_TRY(KK_KV_STORE, launch_talk_queries(m->p0, Nin, L.q_b, L.talk, m->p2, H * Nk, H, G, d, n, st));
     {
       GqaAttnArgs g;
       g.c = c, g.q = m->p2, g.ldq = H * Nk, g.out = m->p1, g.ldo = Ng;
@@ -404,9 +406,9 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       FAM_TRY(KK_F32_NORM, launch_rms_step(s, st));
     } else if (L.kind == 2) {
       const int E = L.experts, top = L.top, ff = L.ff;
-      {  // router logits: fp32
+      {  // router logits: fp32 sums of exact products (in bf16 serving precision the normed row goes in as its bf16 rounding)
         GemmF32 g;
-        g.A = m->hn, g.lda = W, g.W = L.w_router, g.ldw = W, g.C = m->zr, g.ldc = E, g.M = n, g.N = E, g.K = W;
+        g.A = m->hn, g.lda = W, g.W = L.w_router, g.ldw = W, g.C = m->zr, g.ldc = E, g.M = n, g.N = E, g.K = W, g.round_a = rnd;
         FAM_TRY(KK_MOE_ROUTE, launch_gemm_f32(g, st));
       }
       FAM_TRY(KK_MOE_ROUTE, launch_moe_route_sigmoid(m->zr, E, E, top, L.groups, L.keep, L.correction, L.route_scale, m->top_idx, m->top_w, n, st));

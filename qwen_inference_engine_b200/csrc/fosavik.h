@@ -63,7 +63,20 @@ struct KvRowCache {
 // per row: keys k[r, 0:kw] (optionally unit-RMS normed per `norm_dim` consecutive elements, times k_norm) and values
 // v[r, 0:vw] -> cache row (slot, pos).  Rider: the row's queries q[r, 0:q_heads*norm_dim] normed in place with q_norm.
 // Optional: biases added to keys and values first; values blended with another layer's values of the same rows,
-// v = (1 - lam) v + lam v_other (lam one bf16 number on the device); the stored values also kept as fp32 rows (v_keep).
+// v = (1 - lam) v + lam v_other (lam one bf16 number on the device); the stored values also kept as fp32 rows (v_keep);
+// the head-mixed queries of the row (TalkQueries below) written in the same launch.
+// Mixing the heads' scores before the softmax, score'_h = sum_g talk[h, g] score_g, is linear in the queries: with
+// qt[r, h, c * dim + e] = sum over the heads g of kv head c of talk[h, g] * (q[r, g, e] + q_bias[g * dim + e])
+// head h's mixed score against key j is qt[r, h, :] . [keys of all kv heads of j] (GqaAttnArgs::shared_keys), and distance
+// slopes mix the same way (slopes'_h = sum_g talk[h, g] slopes_g, a constant of the layer).  q_bias may be null.
+struct TalkQueries {
+  const float* q = nullptr;
+  int ldq = 0;
+  const bf16* q_bias = nullptr;
+  const bf16* talk = nullptr;  // [heads, heads]; null: no rider
+  float* qt = nullptr;
+  int ldqt = 0, heads = 0, kv_heads = 0, dim = 0;
+};
 struct KvStoreArgs {
   KvRowCache c;
   const float* k = nullptr;
@@ -83,6 +96,7 @@ struct KvStoreArgs {
   int ld_vo = 0;
   float* v_keep = nullptr;
   int ld_vk = 0;
+  TalkQueries tq;
   const int *pos = nullptr, *slot = nullptr, *block_table = nullptr;
   int max_pages = 0, n = 0;
 };
@@ -95,7 +109,7 @@ cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st);
 // slopes (optional, [heads] fp32): slopes[h] * (pos - j) is taken off the scaled score of key j (a linear distance penalty).
 // shared_keys: every head scores against the WHOLE key part of the cached row (dim = kw / maps elements: the keys of all
 // kv heads side by side) while its values stay those of kv head h / (heads / kv_heads); the queries are then
-// [h][map][kw / maps] (launch_talk_queries builds them).
+// [h][map][kw / maps] (TalkQueries builds them).
 // The keys of a row may be split over CTAs; partial (max, sum, acc) go through ws and a second kernel finishes.
 struct GqaAttnArgs {
   KvRowCache c;
@@ -126,12 +140,8 @@ struct GqaAttnArgs {
 // floats of workspace that n rows need with one split
 inline size_t gqa_ws_floats(int n, int heads, int maps, int vdim) { return (size_t)n * heads * maps * (vdim + 2); }
 cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_launches = nullptr);
-// Mixing the heads' scores before the softmax, score'_h = sum_g talk[h, g] score_g, is linear in the queries: with
-// qt[r, h, c * dim + e] = sum over the heads g of kv head c of talk[h, g] * (q[r, g, e] + q_bias[g * dim + e])
-// head h's mixed score against key j is qt[r, h, :] . [keys of all kv heads of j] (shared_keys above), and distance
-// slopes mix the same way (slopes'_h = sum_g talk[h, g] slopes_g, a constant of the layer).  q_bias may be null.
-cudaError_t launch_talk_queries(const float* q, int ldq, const bf16* q_bias, const bf16* talk, float* qt, int ldqt, int heads, int kv_heads, int dim,
-                                int n, cudaStream_t st);
+// the head-mixed queries alone (KvStoreArgs::tq does the same inside the store)
+cudaError_t launch_talk_queries(const TalkQueries& t, int n, cudaStream_t st);
 
 // ---------------------------------------------------------------- short convolution and recurrences (recurrent.cu)
 // Causal per-channel convolution over the rows of each segment: out[t, c] = act(b[c] + sum_i w[c, i] * in(t - (taps-1-i), c)),

@@ -548,7 +548,9 @@ cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
       return vec ? launch_k(gemv_f32_kernel<true>, grid, dim3(256), 0, st, g) : launch_k(gemv_f32_kernel<false>, grid, dim3(256), 0, st, g);
     }
   }
-  if (g.N <= SKINNY_N && !g.w_trans && !g.grp_off && !g.row_idx && g.batches == 1) {
+  // few columns: the fp32 kernel below, unless the operands are bf16 values anyway (round_a) and the rows are many: then the
+  // tensor-core tile kernel is several times faster even with most of its 64 columns idle
+  if (g.N <= SKINNY_N && !g.w_trans && !g.grp_off && !g.row_idx && g.batches == 1 && !(g.round_a && g.M >= 256)) {
     const bool wide = g.N > 32;
     const size_t smem = (size_t)((g.N + 3) & ~3) * (wide ? 512 : 1024) * sizeof(float);  // <= 128 KB
     auto* kern = wide ? gemm_skinny_f32_kernel<64, 8, 512> : gemm_skinny_f32_kernel<32, 16, 1024>;
