@@ -334,3 +334,23 @@ def test_bf16_prompt_attention_on_tensor_cores_keeps_the_edges(tmp_path):
     eb = np.sqrt(((np.concatenate([lg[150:], lg2]) - right[1]) ** 2).mean(-1)) / np.sqrt((right[1] ** 2).mean(-1))
     assert np.median(ea) < tol / 3 and np.quantile(ea, 0.95) < tol, (np.median(ea), ea.max())
     assert np.median(eb) < tol / 3 and np.quantile(eb, 0.95) < tol, (np.median(eb), eb.max())
+
+
+def test_bf16_other_sizes_and_wide_key_rows(tmp_path):
+    # bf16 serving precision away from the tensor-core shapes: a width that is no multiple of 64 (the tile GEMM instead
+    # of tcgen05), key rows of 4 x 40 = 160 elements and values of 136 (beyond the tensor-core attention's tiles: the
+    # per-row kernel serves portions of 64 rows and more, too), portions against the whole prompt
+    layers = [U.attn(heads=4, kv_heads=4, dim=40, vdim=12, window=50, scale=0.3, mlp=U.dense(ff=30)),
+              U.attn(heads=2, kv_heads=1, dim=24, vdim=136, window=0, scale=0.4, v_mix=False, mlp=U.moe(experts=6, top=2, ff=10, shared_ff=20)),
+              U.attn(heads=4, kv_heads=4, dim=40, vdim=12, window=70, scale=0.3, mlp=None)]
+    cfg = U.make_config(layers, width=36, vocab=41)
+    w = U.random_weights(cfg, seed=37)
+    toks = _tokens(cfg, 120, 9)
+    right = _oracle_logits(cfg, w, toks)
+    eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=24, rows=256)
+    whole = _whole(eng, toks)
+    cut = _cuts(eng, toks, [70, 3, 1, 46])
+    eng.close()
+    for got in (whole, cut):
+        err = np.sqrt(((got - right) ** 2).mean(-1)) / np.sqrt((right ** 2).mean(-1))
+        assert np.median(err) < 1e-2 and np.quantile(err, 0.95) < 3e-2, (np.median(err), err.max())
