@@ -30,7 +30,39 @@ __global__ void silu_glu_kernel(const float* gu, int ld, float* out, int ldo, in
   }
 }
 
+__global__ void xielu_bf16_kernel(bf16* __restrict__ z, int ld, int cols, const bf16* __restrict__ pq) {
+  pdl_wait();
+  pdl_trigger();
+  const float ap = softplus_f(bf2f(pq[0])), an = 0.5f + softplus_f(bf2f(pq[1]));
+  bf16* row = z + (size_t)blockIdx.x * ld;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    const float v = bf2f(row[i]);
+    row[i] = f2bf(v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v));
+  }
+}
+
+__global__ void silu_glu_bf16_kernel(const bf16* __restrict__ gu, int ld, bf16* __restrict__ out, int ldo, int ff) {
+  pdl_wait();
+  pdl_trigger();
+  const bf16* row = gu + (size_t)blockIdx.x * ld;
+  bf16* o = out + (size_t)blockIdx.x * ldo;
+  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+    const float g = bf2f(row[i]);
+    o[i] = f2bf(g / (1.0f + expf(-g)) * bf2f(row[ff + i]));
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_xielu_bf16(bf16* z, int ld, int cols, const bf16* pq, int n, cudaStream_t st) {
+  if (n <= 0 || cols <= 0) return cudaSuccess;
+  return launch_k(xielu_bf16_kernel, dim3(n), dim3(256), 0, st, z, ld, cols, pq);
+}
+
+cudaError_t launch_silu_glu_bf16(const bf16* gu, int ld, bf16* out, int ldo, int ff, int n, cudaStream_t st) {
+  if (n <= 0 || ff <= 0) return cudaSuccess;
+  return launch_k(silu_glu_bf16_kernel, dim3(n), dim3(256), 0, st, gu, ld, out, ldo, ff);
+}
 
 cudaError_t launch_xielu(float* z, int ld, int cols, const bf16* pq, int n, cudaStream_t st) {
   if (n <= 0 || cols <= 0) return cudaSuccess;

@@ -504,6 +504,9 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
           v1 = (rv1 ? out1[c + e] : 0.f) - a.lam * v1;
           sq0 = fmaf(v0, v0, sq0), sq1 = fmaf(v1, v1, sq1);
           o[vb][e] = v0, o[vb][2 + e] = v1;
+        } else if (a.out_bf) {
+          if (rv0) a.out_bf[(size_t)(row0 + wrow + qr) * a.ldo_bf + (size_t)h * vd + c + e] = f2bf(v0);
+          if (rv1) a.out_bf[(size_t)(row0 + wrow + qr + 8) * a.ldo_bf + (size_t)h * vd + c + e] = f2bf(v1);
         } else {
           if (rv0) out0[c + e] = v0;
           if (rv1) out1[c + e] = v1;
@@ -599,6 +602,11 @@ __global__ void __launch_bounds__(128) gqa_finish_kernel(const GqaAttnArgs a, in
     for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
     rstd = a.post / sqrtf(t / (float)vd + a.eps);
   }
+  if (a.out_bf) {
+    bf16* ob = a.out_bf + (size_t)r * a.ldo_bf + (size_t)h * vd;
+    for (int c = threadIdx.x; c < vd; c += blockDim.x) ob[c] = f2bf(o[c] * rstd);
+    return;
+  }
   float* out = a.out + (size_t)r * a.ldo + (size_t)h * vd;
   for (int c = threadIdx.x; c < vd; c += blockDim.x) out[c] = o[c] * rstd;
 }
@@ -647,6 +655,7 @@ cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_l
   if (a.n <= 0) return cudaSuccess;
   if (a.shared_keys && (a.maps != 1 || a.dim != a.c.kw)) return cudaErrorInvalidValue;
   if (a.finish == 3 && !a.gate) return cudaErrorInvalidValue;
+  if (a.out_bf && a.maps != 1) return cudaErrorInvalidValue;
   // prompt portions over a bf16 cache: the tensor-core kernel (one launch, no workspace); QIE_ATTN_MMA=0 keeps the per-row kernel (A/B)
   static const bool mma_on = [] { const char* v = getenv("QIE_ATTN_MMA"); return !(v && v[0] == '0'); }();
   if (mma_on && a.seg_start && a.c.elt_bytes == 2 && a.n >= 64 && a.dim <= 128 && a.vdim <= 128 && a.maps <= 2 && a.heads % a.kv_heads == 0 &&

@@ -43,6 +43,11 @@ struct RmsStep {
   const bf16* w_in = nullptr;
   float* h = nullptr;
   const int* gather = nullptr;
+  // bf16 rows around tensor-core GEMMs: y / the shared expert's output given as dense bf16 rows [n, width] (instead of y / mix.ys),
+  // the normed row also (or only) written as dense bf16
+  const bf16* y_bf = nullptr;
+  const bf16* ys_bf = nullptr;
+  bf16* h_bf = nullptr;
 };
 cudaError_t launch_rms_step(const RmsStep& a, cudaStream_t st);
 // Norm + token shift over the rows of each segment: h_t = rms(x_t) w;  out_t = h_t + (h_{t-1} - h_t) * mu, where the row
@@ -55,6 +60,7 @@ struct RmsShiftArgs {
   const bf16* w = nullptr;
   const bf16* mu = nullptr;  // [width]
   float* out = nullptr;
+  bf16* out_bf = nullptr;  // optional dense bf16 copy [n, width] (the operand of a tensor-core GEMM)
   float* carry = nullptr;
   size_t slot_stride = 0;
   const int* seg_start = nullptr;
@@ -67,8 +73,10 @@ cudaError_t launch_rms_shift(const RmsShiftArgs& a, cudaStream_t st);
 // in place over z[r, 0:cols]: xIELU with the two raw parameters pq[0], pq[1]:
 //   z > 0: softplus(pq[0]) z^2 + z / 2;   z <= 0: (1/2 + softplus(pq[1])) (exp(z) - 1 - z) + z / 2
 cudaError_t launch_xielu(float* z, int ld, int cols, const bf16* pq, int n, cudaStream_t st);
+cudaError_t launch_xielu_bf16(bf16* z, int ld, int cols, const bf16* pq, int n, cudaStream_t st);  // bf16 rows, fp32 arithmetic
 // out[r, c] = silu(gu[r, c]) * gu[r, ff + c]
 cudaError_t launch_silu_glu(const float* gu, int ld, float* out, int ldo, int ff, int n, cudaStream_t st);
+cudaError_t launch_silu_glu_bf16(const bf16* gu, int ld, bf16* out, int ldo, int ff, int n, cudaStream_t st);
 
 // ---------------------------------------------------------------- sigmoid router with group-limited choice (moe.cu)
 // s = sigmoid(z[r, 0:experts]); choice score c = s + correction.  The experts form `groups` equal runs of neighbours; a
@@ -124,6 +132,9 @@ struct DxModel : RowFamily {
   int *top_idx = nullptr, *grp_off = nullptr, *perm_row = nullptr, *slot_of = nullptr;
   int vf_width = 0;
   TcProjector tc;
+  // bf16 rows between the producers and consumers of tensor-core GEMMs (bf16 precision): hb normed input, ub / ub2 hidden rows,
+  // yb sublayer output, ysb shared expert output
+  bf16 *hb = nullptr, *ub = nullptr, *ub2 = nullptr, *yb = nullptr, *ysb = nullptr;
   float* attn_ws = nullptr;
   size_t attn_ws_floats = 0;
 };

@@ -185,7 +185,7 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   e->cfg = qie_config{m->width, 0, (int)m->layers.size(), 0, 0, 0, m->vocab, context};
   size_t page_elems = 0, total_heads = 0;
   size_t w0 = 1, w1 = 1, w2 = 1, hmv = 1, maxk = m->width, maxn = m->width;
-  size_t w_zr = 1, w_top = 1, w_he = 1, w_hs = 1;
+  size_t w_zr = 1, w_top = 1, w_he = 1, w_hs = 1, w_ff = 1;
   int max_experts = 0;
   for (const DxLayer& L : m->layers) total_heads += L.heads;
   std::vector<float> slopes(total_heads);
@@ -223,6 +223,7 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
     if (L.kind == 1) {
       L.w_up = P(p + "mlp.up"), L.w_down = P(p + "mlp.down"), L.act = P(p + "mlp.act");
       w0 = std::max(w0, (size_t)L.ff);
+      w_ff = std::max(w_ff, (size_t)L.ff);
       maxk = std::max(maxk, (size_t)L.ff);
       maxn = std::max(maxn, (size_t)L.ff);
     } else {
@@ -279,7 +280,15 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   CUS(cudaMalloc(&m->grp_off, ((size_t)max_experts + 2) * sizeof(int)));
   m->attn_ws_floats = (R + 2048) * hmv;  // room for key splits when a step has few rows
   CUS(fbuf(&m->attn_ws, m->attn_ws_floats));
-  if (!m->f32) CUS(m->tc.alloc(R, maxk, std::max(maxn, (size_t)m->vocab), e->stream));
+  if (!m->f32) {
+    CUS(m->tc.alloc(R, maxk, std::max(maxn, (size_t)m->vocab), e->stream));
+    auto bbuf = [&](bf16** p, size_t n) { return cudaMalloc(p, std::max<size_t>(n, 8) * sizeof(bf16)); };
+    CUS(bbuf(&m->hb, R * W));
+    CUS(bbuf(&m->ub, R * std::max(w_ff, w_hs)));
+    CUS(bbuf(&m->ub2, R * std::max(w1, w_hs / 2 + 1)));
+    CUS(bbuf(&m->yb, R * W));
+    CUS(bbuf(&m->ysb, R * W));
+  }
   CUS(m->alloc_row_buffers(R));
   e->logits_rows = (int)R;
   CUS(cudaStreamSynchronize(e->stream));
@@ -321,7 +330,8 @@ std::string ditenex_create_synthetic(qie_engine* e, const std::string& cfg_json,
 }
 
 void DxModel::release() {
-  void* dev[] = {blob, slopes_all, kv_pool, carry, x, hn, y, p0, p1, p2, vf, zr, top_w, he, hg, ye, hs, ys, xo, top_idx, perm_row, slot_of, grp_off, attn_ws};
+  void* dev[] = {blob, slopes_all, kv_pool, carry, x, hn, y, p0, p1, p2, vf, zr, top_w, he, hg, ye, hs, ys, xo, top_idx, perm_row, slot_of, grp_off, attn_ws,
+                 hb, ub, ub2, yb, ysb};
   tc.release();
   release_row_buffers();
   for (void* p : dev)
@@ -351,18 +361,29 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
   if (m->dump_layers && !m->layer_dump)
     if (cudaMalloc(&m->layer_dump, m->layers.size() * (size_t)e->opts.max_batch_tokens * W * sizeof(float)) != cudaSuccess) return cudaErrorMemoryAllocation;
   FAM_TRY(KK_EMBED, launch_embed_streams(m->x, m->embed, m->pos_table, e->ids_d, e->pos_d, W, 1, n, st));
+  // bf16 precision and a GEMM the tcgen05 kernel takes: its producer writes bf16 rows and its consumer reads them, with
+  // no conversion kernels in between (the same bf16 values as on the fp32-row path: operands and results are rounded once)
+  auto tcfit = [&](int K, int N, const bf16* Wt) { return !m->f32 && m->tc.fits(n, K, N, Wt); };
   for (size_t li = 0; li < m->layers.size(); ++li) {
     const DxLayer& L = m->layers[li];
     const int H = L.heads, G = L.kv_heads, d = L.dim, vd = L.vdim;
     const int Nq = H * d, Nk = G * d, Nv = G * vd, Ng = H * vd, Nin = Nq + Nk + Nv + Ng;
+    const bool tc_in = tcfit(W, Nin, L.w_in), tc_o = tcfit(Ng, W, L.wo);
     {  // input norm + token shift
       RmsShiftArgs s;
-      s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.w = L.norm1, s.mu = L.shift, s.out = m->hn;
+      s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.w = L.norm1, s.mu = L.shift;
+      if (tc_in) s.out_bf = m->hb;
+      else s.out = m->hn;
       s.carry = m->carry + li * (size_t)W, s.slot_stride = m->slot_floats;
       s.seg_start = segs, s.seg_slot = seg_sl, s.n_seg = n_seg;
       FAM_TRY(KK_F32_NORM, launch_rms_shift(s, st));
     }
-    FAM_TRY(KK_F32_PROJ, proj(m->hn, W, L.w_in, W, Nin, m->p0, Nin, n));
+    if (tc_in) {
+      FAM_TRY(KK_F32_PROJ, m->tc.gemm_bf16(e, m->hb, L.w_in, W, Nin, m->tc.cb, n));
+      FAM_TRY(KK_F32_PROJ, launch_rows_bf16_to_f32(m->tc.cb, Nin, m->p0, Nin, 0, n, st));
+    } else {
+      FAM_TRY(KK_F32_PROJ, proj(m->hn, W, L.w_in, W, Nin, m->p0, Nin, n));
+    }
     KvRowCache c;
     c.pool = m->kv_pool, c.elt_bytes = m->f32 ? 4 : 2, c.page_size = e->kv.page_size, c.page_elems = m->page_elems;
     c.layer_off = L.kv_off, c.kw = Nk, c.vw = Nv;
@@ -381,6 +402,7 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
     {
       GqaAttnArgs g;
       g.c = c, g.q = m->p2, g.ldq = H * Nk, g.out = m->p1, g.ldo = Ng;
+      if (tc_o) g.out_bf = m->ub2, g.ldo_bf = Ng;
       g.heads = H, g.kv_heads = G, g.dim = Nk, g.vdim = vd, g.maps = 1, g.scale = L.scale, g.shared_keys = 1, g.slopes = L.slopes;
       g.window = L.window, g.finish = 3, g.gate = m->p0 + Nq + Nk + Nv, g.ldg = Nin, g.eps = m->eps;
       g.pos = e->pos_d, g.slot = e->slot_d, g.block_table = e->block_table_d, g.max_pages = e->max_pages_per_seq, g.n = n, g.max_keys = max_kv_len;
@@ -390,19 +412,43 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       FAM_TRY(KK_GQA_ATTN, launch_gqa_attention(g, st, &nl));
       e->launches += nl > 0 ? nl - 1 : 0;
     }
-    FAM_TRY(KK_F32_PROJ, proj(m->p1, Ng, L.wo, Ng, W, m->y, W, n));
+    if (tc_o) FAM_TRY(KK_F32_PROJ, m->tc.gemm_bf16(e, m->ub2, L.wo, Ng, W, m->yb, n));
+    else FAM_TRY(KK_F32_PROJ, proj(m->p1, Ng, L.wo, Ng, W, m->y, W, n));
+    // which rows the feed-forward's GEMMs want
+    const bool tc_up = L.kind == 1 && tcfit(W, L.ff, L.w_up), tc_down = tc_up && tcfit(L.ff, W, L.w_down);
+    const bool tc_sh = L.kind == 2 && L.shared_ff > 0 && tcfit(W, 2 * L.shared_ff, L.w_sgu) && tcfit(L.shared_ff, W, L.w_sdown);
     {  // x += m * rms(y) norm1b; the same launch norms for the feed-forward
       RmsStep s;
-      s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.y = m->y, s.w_out = L.norm1b, s.mult = m->res_mult;
-      if (L.kind) s.w_in = L.norm2, s.h = m->hn;
+      s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.w_out = L.norm1b, s.mult = m->res_mult;
+      if (tc_o) s.y_bf = m->yb;
+      else s.y = m->y;
+      if (L.kind) {
+        s.w_in = L.norm2;
+        if (tc_up || tc_sh) s.h_bf = m->hb;
+        if (!tc_up) s.h = m->hn;  // the router and the experts read fp32 rows
+      }
       FAM_TRY(KK_F32_NORM, launch_rms_step(s, st));
     }
     if (L.kind == 1) {
-      FAM_TRY(KK_F32_PROJ, proj(m->hn, W, L.w_up, W, L.ff, m->p0, L.ff, n));
-      FAM_TRY(KK_GLU, launch_xielu(m->p0, L.ff, L.ff, L.act, n, st));
-      FAM_TRY(KK_F32_PROJ, proj(m->p0, L.ff, L.w_down, L.ff, W, m->y, W, n));
       RmsStep s;
-      s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.y = m->y, s.w_out = L.norm2b, s.mult = m->res_mult;
+      s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.w_out = L.norm2b, s.mult = m->res_mult;
+      if (tc_up) {
+        FAM_TRY(KK_F32_PROJ, m->tc.gemm_bf16(e, m->hb, L.w_up, W, L.ff, m->ub, n));
+        FAM_TRY(KK_GLU, launch_xielu_bf16(m->ub, L.ff, L.ff, L.act, n, st));
+        if (tc_down) {
+          FAM_TRY(KK_F32_PROJ, m->tc.gemm_bf16(e, m->ub, L.w_down, L.ff, W, m->yb, n));
+          s.y_bf = m->yb;
+        } else {
+          FAM_TRY(KK_F32_PROJ, launch_rows_bf16_to_f32(m->ub, L.ff, m->p0, L.ff, 0, n, st));
+          FAM_TRY(KK_F32_PROJ, proj(m->p0, L.ff, L.w_down, L.ff, W, m->y, W, n));
+          s.y = m->y;
+        }
+      } else {
+        FAM_TRY(KK_F32_PROJ, proj(m->hn, W, L.w_up, W, L.ff, m->p0, L.ff, n));
+        FAM_TRY(KK_GLU, launch_xielu(m->p0, L.ff, L.ff, L.act, n, st));
+        FAM_TRY(KK_F32_PROJ, proj(m->p0, L.ff, L.w_down, L.ff, W, m->y, W, n));
+        s.y = m->y;
+      }
       FAM_TRY(KK_F32_NORM, launch_rms_step(s, st));
     } else if (L.kind == 2) {
       const int E = L.experts, top = L.top, ff = L.ff;
@@ -424,15 +470,23 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
         g2.M = n * top, g2.N = W, g2.K = ff, g2.batches = E, g2.grp_off = m->grp_off, g2.round_a = rnd;
         FAM_TRY(KK_MOE_EXPERTS, launch_gemm_f32(g2, st));
       }
-      if (L.shared_ff > 0) {
-        const int sf = L.shared_ff;
-        FAM_TRY(KK_MOE_SHARED, proj(m->hn, W, L.w_sgu, W, 2 * sf, m->hs, 2 * sf, n));
-        FAM_TRY(KK_GLU, launch_silu_glu(m->hs, 2 * sf, m->hs, 2 * sf, sf, n, st));
-        FAM_TRY(KK_MOE_SHARED, proj(m->hs, 2 * sf, L.w_sdown, sf, W, m->ys, W, n));
-      }
       RmsStep s;  // the combine of the experts rides the output norm
       s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.w_out = L.norm2b, s.mult = m->res_mult;
-      s.mix.ye = m->ye, s.mix.slot_of = m->slot_of, s.mix.top_w = m->top_w, s.mix.top = top, s.mix.ys = L.shared_ff > 0 ? m->ys : nullptr;
+      s.mix.ye = m->ye, s.mix.slot_of = m->slot_of, s.mix.top_w = m->top_w, s.mix.top = top;
+      if (L.shared_ff > 0) {
+        const int sf = L.shared_ff;
+        if (tc_sh) {
+          FAM_TRY(KK_MOE_SHARED, m->tc.gemm_bf16(e, m->hb, L.w_sgu, W, 2 * sf, m->ub, n));
+          FAM_TRY(KK_GLU, launch_silu_glu_bf16(m->ub, 2 * sf, m->ub2, sf, sf, n, st));
+          FAM_TRY(KK_MOE_SHARED, m->tc.gemm_bf16(e, m->ub2, L.w_sdown, sf, W, m->ysb, n));
+          s.ys_bf = m->ysb;
+        } else {
+          FAM_TRY(KK_MOE_SHARED, proj(m->hn, W, L.w_sgu, W, 2 * sf, m->hs, 2 * sf, n));
+          FAM_TRY(KK_GLU, launch_silu_glu(m->hs, 2 * sf, m->hs, 2 * sf, sf, n, st));
+          FAM_TRY(KK_MOE_SHARED, proj(m->hs, 2 * sf, L.w_sdown, sf, W, m->ys, W, n));
+          s.mix.ys = m->ys;
+        }
+      }
       FAM_TRY(KK_F32_NORM, launch_rms_step(s, st));
     }
     if (m->dump_layers)

@@ -89,6 +89,8 @@ struct TcProjector {
   void release();
   bool fits(int n, int K, int N, const bf16* W) const;
   cudaError_t gemm(qie_engine* e, const float* A, int lda, const bf16* W, int K, int N, float* C, int ldc, int act, int n);
+  // the GEMM alone, for callers whose producers write bf16 rows and whose consumers read them: A dense [n, K] -> C dense [n, N]
+  cudaError_t gemm_bf16(qie_engine* e, const bf16* A, const bf16* W, int K, int N, bf16* C, int n);
 };
 
 }  // namespace qie

@@ -145,6 +145,14 @@ bool TcProjector::fits(int n, int K, int N, const bf16* W) const {
 }
 
 cudaError_t TcProjector::gemm(qie_engine* e, const float* A, int lda, const bf16* W, int K, int N, float* C, int ldc, int act, int n) {
+  cudaError_t r = launch_rows_f32_to_bf16(A, lda, nullptr, ab, K, n, e->stream);
+  if (r != cudaSuccess) return r;
+  if ((r = gemm_bf16(e, ab, W, K, N, cb, n)) != cudaSuccess) return r;
+  ++e->launches;
+  return launch_rows_bf16_to_f32(cb, N, C, ldc, act, n, e->stream);
+}
+
+cudaError_t TcProjector::gemm_bf16(qie_engine* e, const bf16* A, const bf16* W, int K, int N, bf16* C, int n) {
   cudaStream_t st = e->stream;
   auto* mp = static_cast<std::map<const bf16*, TensorMap2D>*>(maps);
   auto it = mp->find(W);
@@ -154,10 +162,9 @@ cudaError_t TcProjector::gemm(qie_engine* e, const float* A, int lda, const bf16
     if (r != cudaSuccess) return r;
     it = mp->emplace(W, wm).first;
   }
-  cudaError_t r = launch_rows_f32_to_bf16(A, lda, nullptr, ab, K, n, st);
-  if (r != cudaSuccess) return r;
+  cudaError_t r;
   TensorMap2D xmap;
-  if ((r = make_tensor_map_2d(&xmap, ab, n, K, tc_token_tile(n))) != cudaSuccess) return r;
+  if ((r = make_tensor_map_2d(&xmap, A, n, K, tc_token_tile(n))) != cudaSuccess) return r;
   TcGemm t{};
   t.w[0] = &it->second;
   t.rows[0] = N;
@@ -166,18 +173,18 @@ cudaError_t TcProjector::gemm(qie_engine* e, const float* A, int lda, const bf16
   t.M = n;
   t.K = K;
   t.epi = EPI_STORE;
-  t.out = cb;
+  t.out = C;
   t.ld_out = N;
   t.ws = ws;
   t.ws_bytes = ws_bytes;
   t.max_splits = (int)std::max<size_t>(1, ws_bytes / ((size_t)n * N * sizeof(float)));
   t.counters = counters;
   t.n_counters = 8192;
-  t.w_static = 0;  // the operand comes from the conversion kernel in front
+  t.w_static = 0;  // the operand comes from the kernel in front
   int nl = 0;
   if ((r = launch_gemm_tcgen05(t, e->num_sms, st, &nl)) != cudaSuccess) return r;
-  e->launches += nl + 1;
-  return launch_rows_bf16_to_f32(cb, N, C, ldc, act, n, st);
+  e->launches += nl > 0 ? nl - 1 : 0;  // the caller counts one
+  return cudaSuccess;
 }
 
 }  // namespace qie

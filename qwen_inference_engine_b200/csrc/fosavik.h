@@ -117,6 +117,8 @@ struct GqaAttnArgs {
   int ldq = 0;
   float* out = nullptr;
   int ldo = 0;
+  bf16* out_bf = nullptr;  // maps == 1: the result goes here as bf16 rows (row stride ldo_bf) instead of `out`
+  int ldo_bf = 0;
   int heads = 0, kv_heads = 0, dim = 0, vdim = 0, maps = 1;
   float scale = 1.f;
   int window = 0, keep_first = 0, unit_sink = 0;

@@ -25,26 +25,28 @@ __global__ void __launch_bounds__(256) rms_step_kernel(const RmsStep a) {
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x, W = a.width;
-  const bool add = a.y || a.mix.ye;
+  const bool add = a.y || a.y_bf || a.mix.ye;
   const int src = a.gather ? a.gather[r] : r;  // the add half is never combined with a gather
   float* xr = a.x + (size_t)src * W;
   float sq = 0.f;
   if (add) {
     float s = 0.f;
-    if (a.y) {
+    if (a.y || a.y_bf) {
       const float* y = a.y + (size_t)r * W;
+      const bf16* yb = a.y_bf + (size_t)r * W;
       for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float v = y[i];
+        const float v = a.y_bf ? bf2f(yb[i]) : y[i];
         row[i] = v;
         s = fmaf(v, v, s);
       }
     } else {  // the chosen experts' outputs of this row, weighted, plus the shared expert (gated only when mix.z is given)
       const MoeMix& m = a.mix;
-      const float sg = m.ys ? (m.z ? 1.0f / (1.0f + expf(-m.z[(size_t)r * m.ldz + m.gate_col])) : 1.0f) : 0.f;
+      const bool shared = m.ys || a.ys_bf;
+      const float sg = shared ? (m.z ? 1.0f / (1.0f + expf(-m.z[(size_t)r * m.ldz + m.gate_col])) : 1.0f) : 0.f;
       for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float v = 0.f;
         for (int k = 0; k < m.top; ++k) v = fmaf(m.top_w[(size_t)r * m.top + k], m.ye[(size_t)m.slot_of[(size_t)r * m.top + k] * W + i], v);
-        if (m.ys) v = fmaf(sg, m.ys[(size_t)r * W + i], v);
+        if (shared) v = fmaf(sg, a.ys_bf ? bf2f(a.ys_bf[(size_t)r * W + i]) : m.ys[(size_t)r * W + i], v);
         row[i] = v;
         s = fmaf(v, v, s);
       }
@@ -56,17 +58,20 @@ __global__ void __launch_bounds__(256) rms_step_kernel(const RmsStep a) {
       row[i] = v;
       sq = fmaf(v, v, sq);
     }
-  } else if (a.h) {
+  } else if (a.h || a.h_bf) {
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       const float v = xr[i];
       row[i] = v;
       sq = fmaf(v, v, sq);
     }
   }
-  if (!a.h) return;
+  if (!a.h && !a.h_bf) return;
   const float rstd = 1.0f / sqrtf(block_sum_r(sq, red) / (float)W + a.eps);
-  float* h = a.h + (size_t)r * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) h[i] = row[i] * rstd * bf2f(a.w_in[i]);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = row[i] * rstd * bf2f(a.w_in[i]);
+    if (a.h) a.h[(size_t)r * W + i] = v;
+    if (a.h_bf) a.h_bf[(size_t)r * W + i] = f2bf(v);
+  }
 }
 
 // one CTA per row.  The CTA of a segment's first row also moves the segment's last normed row into the carried row:
@@ -101,7 +106,9 @@ __global__ void __launch_bounds__(256) rms_shift_kernel(const RmsShiftArgs a) {
     const float w = bf2f(a.w[i]);
     const float h = xr[i] * r0 * w, o = xp[i] * r1 * w;
     const float before = head ? carry[i] : o;
-    out[i] = h + (before - h) * bf2f(a.mu[i]);
+    const float v = h + (before - h) * bf2f(a.mu[i]);
+    if (a.out) out[i] = v;
+    if (a.out_bf) a.out_bf[(size_t)r * W + i] = f2bf(v);
     if (head) carry[i] = o;
   }
 }
@@ -110,8 +117,8 @@ __global__ void __launch_bounds__(256) rms_shift_kernel(const RmsShiftArgs a) {
 
 cudaError_t launch_rms_step(const RmsStep& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;
-  const bool add = a.y || a.mix.ye;
-  if ((add && (!a.w_out || a.gather)) || (a.h && !a.w_in) || (!add && !a.h)) return cudaErrorInvalidValue;
+  const bool add = a.y || a.y_bf || a.mix.ye, read = a.h || a.h_bf;
+  if ((add && (!a.w_out || a.gather)) || (read && !a.w_in) || (!add && !read)) return cudaErrorInvalidValue;
   const size_t smem = (size_t)a.width * sizeof(float);
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
