@@ -164,7 +164,12 @@ cudaError_t TcProjector::gemm_bf16(qie_engine* e, const bf16* A, const bf16* W, 
   }
   cudaError_t r;
   TensorMap2D xmap;
-  if ((r = make_tensor_map_2d(&xmap, A, n, K, tc_token_tile(n))) != cudaSuccess) return r;
+  // many rows but few output columns (N = 1024 at 2048 rows: 64 tiles of 128 x 256): half-size token tiles fill the SMs without
+  // the split over K and its reduction through the cluster
+  int tile = tc_token_tile(n);
+  static const bool small_on = [] { const char* v = getenv("QIE_TC_TILE128"); return !(v && v[0] == '0'); }();
+  if (small_on && tile == 256 && (long)((N + 127) / 128) * ((n + 255) / 256) * 2 <= e->num_sms) tile = 128;
+  if ((r = make_tensor_map_2d(&xmap, A, n, K, tile)) != cudaSuccess) return r;
   TcGemm t{};
   t.w[0] = &it->second;
   t.rows[0] = N;
@@ -180,6 +185,7 @@ cudaError_t TcProjector::gemm_bf16(qie_engine* e, const bf16* A, const bf16* W, 
   t.max_splits = (int)std::max<size_t>(1, ws_bytes / ((size_t)n * N * sizeof(float)));
   t.counters = counters;
   t.n_counters = 8192;
+  t.token_tile = tile;
   t.w_static = 0;  // the operand comes from the kernel in front
   int nl = 0;
   if ((r = launch_gemm_tcgen05(t, e->num_sms, st, &nl)) != cudaSuccess) return r;

@@ -869,7 +869,8 @@ cudaError_t launch_gemm_tcgen05(const TcGemm& t, int num_sms, cudaStream_t st, i
   (void)cols;
   g.n_tiles = tiles;
   g.kb_total = (t.K + BK - 1) / BK;
-  const int BN = tc_token_tile(t.M);
+  const int BN = t.token_tile ? t.token_tile : tc_token_tile(t.M);
+  if (BN != 16 && BN != 32 && BN != 64 && BN != 128 && BN != 256) return cudaErrorInvalidValue;
   const int token_tiles = (t.M + BN - 1) / BN;
   // split-K (= cluster size along grid.y) so that roughly one CTA lands on every SM; every
   // slice keeps >= 2 k-blocks; cluster size <= 8 (the portable maximum)

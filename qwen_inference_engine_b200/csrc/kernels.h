@@ -154,6 +154,7 @@ struct TcGemm {
   int* counters;   // zero-initialised ints for the fused split-K reduction (nullptr: separate finalize kernel)
   int n_counters;
   int w_static;    // weights are not produced by a preceding kernel: prefetch them before the PDL wait
+  int token_tile;  // 0: tc_token_tile(M); else the box rows the caller built the activation map with (16, 32, 64, 128 or 256)
 };
 cudaError_t launch_gemm_tcgen05(const TcGemm& t, int num_sms, cudaStream_t st, int* launches);
 
