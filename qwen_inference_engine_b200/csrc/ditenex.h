@@ -135,6 +135,7 @@ struct DxModel : RowFamily {
   // bf16 rows between the producers and consumers of tensor-core GEMMs (bf16 precision): hb normed input, ub / ub2 hidden rows,
   // yb sublayer output, ysb shared expert output
   bf16 *hb = nullptr, *ub = nullptr, *ub2 = nullptr, *yb = nullptr, *ysb = nullptr;
+  bf16* hgb = nullptr;  // gated hidden rows of the experts, grouped by expert
   float* attn_ws = nullptr;
   size_t attn_ws_floats = 0;
 };

@@ -288,6 +288,7 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
     CUS(bbuf(&m->ub2, R * std::max(w1, w_hs / 2 + 1)));
     CUS(bbuf(&m->yb, R * W));
     CUS(bbuf(&m->ysb, R * W));
+    CUS(bbuf(&m->hgb, R * w_he / 2 + 8));
   }
   CUS(m->alloc_row_buffers(R));
   e->logits_rows = (int)R;
@@ -331,7 +332,7 @@ std::string ditenex_create_synthetic(qie_engine* e, const std::string& cfg_json,
 
 void DxModel::release() {
   void* dev[] = {blob, slopes_all, kv_pool, carry, x, hn, y, p0, p1, p2, vf, zr, top_w, he, hg, ye, hs, ys, xo, top_idx, perm_row, slot_of, grp_off, attn_ws,
-                 hb, ub, ub2, yb, ysb};
+                 hb, ub, ub2, yb, ysb, hgb};
   tc.release();
   release_row_buffers();
   for (void* p : dev)
@@ -417,6 +418,16 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
     // which rows the feed-forward's GEMMs want
     const bool tc_up = L.kind == 1 && tcfit(W, L.ff, L.w_up), tc_down = tc_up && tcfit(L.ff, W, L.w_down);
     const bool tc_sh = L.kind == 2 && L.shared_ff > 0 && tcfit(W, 2 * L.shared_ff, L.w_sgu) && tcfit(L.shared_ff, W, L.w_sdown);
+    // the experts' GEMMs over bf16 rows on the tensor-core tile kernel (more rows than the GEMV serves)
+    GroupedGemmBf16 eg, ed;
+    bool tc_ex = false;
+    if (L.kind == 2 && !m->f32 && n * L.top > 16 * 16) {
+      eg.A = m->hb, eg.lda = W, eg.row_idx = m->perm_row, eg.grp_off = m->grp_off, eg.W = L.w_egu, eg.w_batch = (long)2 * L.ff * W;
+      eg.N = 2 * L.ff, eg.K = W, eg.groups = L.experts, eg.rows = n * L.top, eg.gated = 1, eg.out_bf = m->hgb, eg.ldo = L.ff;
+      ed.A = m->hgb, ed.lda = L.ff, ed.grp_off = m->grp_off, ed.W = L.w_edown, ed.w_batch = (long)W * L.ff;
+      ed.N = W, ed.K = L.ff, ed.groups = L.experts, ed.rows = n * L.top, ed.out = m->ye, ed.ldo = W;
+      tc_ex = grouped_gemm_bf16_fits(eg) && grouped_gemm_bf16_fits(ed);
+    }
     {  // x += m * rms(y) norm1b; the same launch norms for the feed-forward
       RmsStep s;
       s.x = m->x, s.width = W, s.n = n, s.eps = m->eps, s.w_out = L.norm1b, s.mult = m->res_mult;
@@ -424,7 +435,7 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       else s.y = m->y;
       if (L.kind) {
         s.w_in = L.norm2;
-        if (tc_up || tc_sh) s.h_bf = m->hb;
+        if (tc_up || tc_sh || tc_ex) s.h_bf = m->hb;
         if (!tc_up) s.h = m->hn;  // the router and the experts read fp32 rows
       }
       FAM_TRY(KK_F32_NORM, launch_rms_step(s, st));
@@ -459,7 +470,10 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       }
       FAM_TRY(KK_MOE_ROUTE, launch_moe_route_sigmoid(m->zr, E, E, top, L.groups, L.keep, L.correction, L.route_scale, m->top_idx, m->top_w, n, st));
       FAM_TRY(KK_MOE_ROUTE, launch_moe_group(m->top_idx, n * top, top, E, m->grp_off, m->perm_row, m->slot_of, st));
-      {
+      if (tc_ex) {
+        FAM_TRY(KK_MOE_EXPERTS, launch_grouped_gemm_bf16(eg, st));
+        FAM_TRY(KK_MOE_EXPERTS, launch_grouped_gemm_bf16(ed, st));
+      } else {
         GemmF32 g;  // [gate | up] of every assignment, rows grouped by expert and gathered from hn
         g.A = m->hn, g.lda = W, g.W = L.w_egu, g.ldw = W, g.w_batch = (long)2 * ff * W, g.C = m->he, g.ldc = 2 * ff;
         g.M = n * top, g.N = 2 * ff, g.K = W, g.batches = E, g.grp_off = m->grp_off, g.row_idx = m->perm_row, g.round_a = rnd;

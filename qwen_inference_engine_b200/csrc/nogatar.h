@@ -143,6 +143,26 @@ cudaError_t launch_moe_group(const int* top_idx, int n_assign, int top, int expe
 cudaError_t launch_moe_combine(const float* ye, const int* slot_of, const float* top_w, int top, const float* ys, const float* z, int ldz,
                                int gate_col, float* y, int width, int n, cudaStream_t st);
 
+// Expert GEMMs on tensor cores over bf16 rows (gemm_grouped.cu): C[row, :] = A[src(row), :] W_z^T for the rows
+// grp_off[z] .. grp_off[z + 1] - 1 of expert z, src(row) = row_idx ? row_idx[row] : row; W_z = W + z * w_batch, [N, K] row-major.
+// gated: W_z = [gate rows | up rows] (N = 2 ff) and out_bf[row, c] = bf16(silu(gate_c) * up_c), c < ff; else out[row, n] fp32.
+struct GroupedGemmBf16 {
+  const bf16* A = nullptr;
+  int lda = 0;
+  const int* row_idx = nullptr;
+  const int* grp_off = nullptr;
+  const bf16* W = nullptr;
+  long w_batch = 0;
+  int N = 0, K = 0, groups = 0;
+  int rows = 0;  // rows over all groups (bounds the grid)
+  int gated = 0;
+  float* out = nullptr;
+  bf16* out_bf = nullptr;
+  int ldo = 0;
+};
+bool grouped_gemm_bf16_fits(const GroupedGemmBf16& g);  // K a multiple of 32, 16-byte aligned rows
+cudaError_t launch_grouped_gemm_bf16(const GroupedGemmBf16& g, cudaStream_t st);
+
 // ---------------------------------------------------------------- the model (nogatar_model.cu)
 struct NgRot {
   int dims = 0;

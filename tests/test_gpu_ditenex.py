@@ -310,10 +310,11 @@ def test_greedy_generation_through_engine_and_scheduler(tmp_path):
 
 def test_bf16_prompt_attention_on_tensor_cores_keeps_the_edges(tmp_path):
     # portions of 64 rows and more over the bf16 cache run 64 rows at a time on tensor cores: a window edge that falls
-    # inside a 64-key block, two sequences of unequal length in one batch, key rows that are padded (2 x 24 -> 64) and
-    # projections wide enough for the tcgen05 GEMM.  The tolerance is bf16's; the fault it guards against is far larger.
+    # inside a 64-key block, two sequences of unequal length in one batch, key rows that are padded (2 x 24 -> 64),
+    # projections wide enough for the tcgen05 GEMM and experts that take the grouped tensor-core GEMM (tiles wider than
+    # the 32 gated columns and the 64 output columns).  The tolerance is bf16's; the fault it guards against is far larger.
     layers = [U.attn(heads=4, kv_heads=2, dim=24, vdim=20, window=37, scale=0.6, mlp=U.dense(ff=128)),
-              U.attn(heads=4, kv_heads=2, dim=16, vdim=20, window=70, scale=0.5, mlp=U.moe(experts=6, top=2, ff=16, shared_ff=64))]
+              U.attn(heads=4, kv_heads=2, dim=16, vdim=20, window=70, scale=0.5, mlp=U.moe(experts=6, top=2, ff=32, shared_ff=64))]
     cfg = U.make_config(layers, width=64, vocab=29)
     w = U.random_weights(cfg, seed=31, gain=1.5)
     U.set_values(w, "l0.shift", np.zeros(64))
