@@ -32,6 +32,16 @@ namespace qie {
 //   add  (y != null or mix.ye != null):  x[r] += mult * rms(y[r]) w_out      (y may be the mixture-of-experts combine
 //                                        of the row, computed on the fly from `mix`; mix.z == null: shared expert ungated)
 //   read (h != null):                    h[r] = rms(x[src(r)]) w_in,  src(r) = gather ? gather[r] : r
+// Rider of the read half in front of a mixture of experts: the row's router logits z_e = w_router[e, :] . h (fp32, from the
+// normed row while it is in shared memory) and the choice of launch_moe_route_sigmoid below, by the same CTA.
+struct RouteRider {
+  const bf16* w_router = nullptr;  // [experts, width]; null: no rider
+  const bf16* correction = nullptr;
+  int experts = 0, top = 0, groups = 1, keep = 1;
+  float scale = 1.f;
+  int* top_idx = nullptr;  // [n, top]
+  float* top_w = nullptr;
+};
 struct RmsStep {
   float* x = nullptr;
   int width = 0, n = 0;
@@ -48,6 +58,7 @@ struct RmsStep {
   const bf16* y_bf = nullptr;
   const bf16* ys_bf = nullptr;
   bf16* h_bf = nullptr;
+  RouteRider route;
 };
 cudaError_t launch_rms_step(const RmsStep& a, cudaStream_t st);
 // Norm + token shift over the rows of each segment: h_t = rms(x_t) w;  out_t = h_t + (h_{t-1} - h_t) * mu, where the row

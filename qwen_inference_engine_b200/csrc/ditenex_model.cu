@@ -436,7 +436,11 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       if (L.kind) {
         s.w_in = L.norm2;
         if (tc_up || tc_sh || tc_ex) s.h_bf = m->hb;
-        if (!tc_up) s.h = m->hn;  // the router and the experts read fp32 rows
+        if (!tc_up) s.h = m->hn;  // the experts' GEMV reads fp32 rows
+        if (L.kind == 2) {  // the router's logits and choice ride this launch
+          s.route.w_router = L.w_router, s.route.correction = L.correction, s.route.experts = L.experts, s.route.top = L.top;
+          s.route.groups = L.groups, s.route.keep = L.keep, s.route.scale = L.route_scale, s.route.top_idx = m->top_idx, s.route.top_w = m->top_w;
+        }
       }
       FAM_TRY(KK_F32_NORM, launch_rms_step(s, st));
     }
@@ -463,12 +467,6 @@ cudaError_t DxModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       FAM_TRY(KK_F32_NORM, launch_rms_step(s, st));
     } else if (L.kind == 2) {
       const int E = L.experts, top = L.top, ff = L.ff;
-      {  // router logits: fp32 sums of exact products (in bf16 serving precision the normed row goes in as its bf16 rounding)
-        GemmF32 g;
-        g.A = m->hn, g.lda = W, g.W = L.w_router, g.ldw = W, g.C = m->zr, g.ldc = E, g.M = n, g.N = E, g.K = W, g.round_a = rnd;
-        FAM_TRY(KK_MOE_ROUTE, launch_gemm_f32(g, st));
-      }
-      FAM_TRY(KK_MOE_ROUTE, launch_moe_route_sigmoid(m->zr, E, E, top, L.groups, L.keep, L.correction, L.route_scale, m->top_idx, m->top_w, n, st));
       FAM_TRY(KK_MOE_ROUTE, launch_moe_group(m->top_idx, n * top, top, E, m->grp_off, m->perm_row, m->slot_of, st));
       if (tc_ex) {
         FAM_TRY(KK_MOE_EXPERTS, launch_grouped_gemm_bf16(eg, st));

@@ -5,6 +5,7 @@
 // the grouped buffers does, the values stored there do not).
 #include "ditenex.h"
 #include "launch.h"
+#include "moe_route.cuh"
 #include "nogatar.h"
 
 namespace qie {
@@ -66,24 +67,7 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int exper
   }
 }
 
-// Sigmoid router with a choice correction and group-limited top-k (ditenex.h).  One warp per row; shared memory per
-// warp: choice scores [experts] | plain scores [experts] | group scores [groups] | kept marks [groups].
-__device__ __forceinline__ int warp_argmax_first(const float* v, int count, int lane) {
-  // the largest value, the lowest index among equals; every lane returns the winner
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int e = lane; e < count; e += 32) {
-    const float x = v[e];
-    if (bi == 0x7fffffff || x > bv) bv = x, bi = e;  // ascending e within a lane
-  }
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) bv = ov, bi = oi;
-  }
-  return bi;
-}
-
+// Sigmoid router with a choice correction and group-limited top-k (ditenex.h, moe_route.cuh).  One warp per row.
 __global__ void moe_route_sigmoid_kernel(const float* __restrict__ z, int ldz, int experts, int top, int groups, int keep,
                                          const bf16* __restrict__ correction, float scale, int* __restrict__ top_idx, float* __restrict__ top_w, int n) {
   extern __shared__ float sc[];
@@ -92,51 +76,8 @@ __global__ void moe_route_sigmoid_kernel(const float* __restrict__ z, int ldz, i
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * (blockDim.x >> 5) + w;
   if (r >= n) return;
-  float* c = sc + (size_t)w * (2 * experts + 2 * groups);
-  float* s = c + experts;
-  float* gs = s + experts;
-  float* kept = gs + groups;
-  const float* zr = z + (size_t)r * ldz;
-  for (int e = lane; e < experts; e += 32) {
-    const float v = 1.0f / (1.0f + expf(-zr[e]));
-    s[e] = v;
-    c[e] = v + (correction ? bf2f(correction[e]) : 0.f);
-  }
-  __syncwarp();
-  if (keep < groups) {
-    const int per = experts / groups;
-    for (int g = lane; g < groups; g += 32) {  // the two largest choice scores of the group
-      float a = -INFINITY, b = -INFINITY;
-      for (int e = g * per; e < (g + 1) * per; ++e) {
-        const float x = c[e];
-        if (x > a) b = a, a = x;
-        else if (x > b) b = x;
-      }
-      gs[g] = per > 1 ? a + b : a;
-      kept[g] = 0.f;
-    }
-    __syncwarp();
-    for (int k = 0; k < keep; ++k) {
-      const int bi = warp_argmax_first(gs, groups, lane);
-      __syncwarp();
-      if (lane == 0) gs[bi] = -INFINITY, kept[bi] = 1.f;
-      __syncwarp();
-    }
-    // experts of the other groups drop out of the choice (not merely to zero: choice scores may be negative)
-    for (int e = lane; e < experts; e += 32)
-      if (kept[e / per] == 0.f) c[e] = -INFINITY;
-    __syncwarp();
-  }
-  for (int k = 0; k < top; ++k) {
-    const int bi = warp_argmax_first(c, experts, lane);
-    __syncwarp();
-    if (lane == 0) {
-      top_idx[(size_t)r * top + k] = bi;
-      top_w[(size_t)r * top + k] = s[bi] * scale;
-      c[bi] = -INFINITY;
-    }
-    __syncwarp();
-  }
+  route_sigmoid_row(z + (size_t)r * ldz, sc + (size_t)w * route_scratch_floats(experts, groups), experts, top, groups, keep, correction, scale,
+                    top_idx + (size_t)r * top, top_w + (size_t)r * top, lane);
 }
 
 // one CTA; warp w serves experts w, w + nw, ...: an ordered compaction of the assignments that chose the expert
@@ -217,7 +158,7 @@ cudaError_t launch_moe_route_sigmoid(const float* z, int ldz, int experts, int t
                                      int* top_idx, float* top_w, int n, cudaStream_t st) {
   if (n <= 0) return cudaSuccess;
   if (experts <= 0 || top <= 0 || top > experts || groups <= 0 || experts % groups || keep <= 0 || keep > groups) return cudaErrorInvalidValue;
-  const size_t per_warp = ((size_t)2 * experts + 2 * (size_t)groups) * sizeof(float);
+  const size_t per_warp = route_scratch_floats(experts, groups) * sizeof(float);
   int warps = 8;
   while (warps > 1 && warps * per_warp > 40 * 1024) warps /= 2;
   if (warps * per_warp > 48 * 1024) return cudaErrorInvalidValue;

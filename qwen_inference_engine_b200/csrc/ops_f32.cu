@@ -491,18 +491,30 @@ __global__ void rows_bf16_to_f32_kernel(const bf16* __restrict__ in, int cols, f
   }
 }
 
-// one CTA per row: the largest logit, the lowest index among equals
-__global__ void argmax_f32_kernel(const float* __restrict__ z, int* __restrict__ out, int vocab) {
-  __shared__ float bv[8];
-  __shared__ int bi[8];
+// one CTA per row: the largest logit, the lowest index among equals.  A thread walks its elements in ascending index (four
+// at a time when the row allows 16-byte loads) and keeps the first of equal values; the tree prefers the lower index.
+__global__ void __launch_bounds__(1024) argmax_f32_kernel(const float* __restrict__ z, int* __restrict__ out, int vocab) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
   pdl_wait();
   pdl_trigger();
   const float* row = z + (size_t)blockIdx.x * vocab;
   float v = -INFINITY;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float x = row[i];
-    if (x > v) v = x, idx = i;
+  if (vocab % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+      const float4 x = row4[i];
+      if (x.x > v) v = x.x, idx = 4 * i;
+      if (x.y > v) v = x.y, idx = 4 * i + 1;
+      if (x.z > v) v = x.z, idx = 4 * i + 2;
+      if (x.w > v) v = x.w, idx = 4 * i + 3;
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float x = row[i];
+      if (x > v) v = x, idx = i;
+    }
   }
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, v, o);
@@ -511,10 +523,16 @@ __global__ void argmax_f32_kernel(const float* __restrict__ z, int* __restrict__
   }
   if ((threadIdx.x & 31) == 0) bv[threadIdx.x >> 5] = v, bi[threadIdx.x >> 5] = idx;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-      if (bv[w] > v || (bv[w] == v && bi[w] < idx)) v = bv[w], idx = bi[w];
-    out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    v = threadIdx.x < nw ? bv[threadIdx.x] : -INFINITY;
+    idx = threadIdx.x < nw ? bi[threadIdx.x] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > v || (ov == v && oi < idx)) v = ov, idx = oi;
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
   }
 }
 
@@ -532,7 +550,7 @@ cudaError_t launch_rows_bf16_to_f32(const bf16* in, int cols, float* out, int ld
 
 cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, cudaStream_t st) {
   if (n_rows <= 0) return cudaSuccess;
-  return launch_k(argmax_f32_kernel, dim3(n_rows), dim3(256), 0, st, z, out, vocab);
+  return launch_k(argmax_f32_kernel, dim3(n_rows), dim3(vocab >= 8192 ? 1024 : 256), 0, st, z, out, vocab);
 }
 
 cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {

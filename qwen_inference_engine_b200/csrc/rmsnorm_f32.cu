@@ -4,6 +4,7 @@
 // every reduction in a fixed order per row, so a row's result does not depend on the rows it shares a launch with.
 #include "ditenex.h"
 #include "launch.h"
+#include "moe_route.cuh"
 
 namespace qie {
 namespace {
@@ -71,7 +72,35 @@ __global__ void __launch_bounds__(256) rms_step_kernel(const RmsStep a) {
     const float v = row[i] * rstd * bf2f(a.w_in[i]);
     if (a.h) a.h[(size_t)r * W + i] = v;
     if (a.h_bf) a.h_bf[(size_t)r * W + i] = f2bf(v);
+    row[i] = v;
   }
+  if (!a.route.w_router) return;
+  // router logits of the row: a warp per expert, lanes stride the width (16-byte weight loads when the rows allow it)
+  const RouteRider& rt = a.route;
+  float* zl = row + W;  // [experts] logits, then the router's scratch
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const bool vec = W % 8 == 0 && (reinterpret_cast<uintptr_t>(rt.w_router) & 15) == 0;
+  for (int e = warp; e < rt.experts; e += nw) {
+    const bf16* wr = rt.w_router + (size_t)e * W;
+    float acc = 0.f;
+    if (vec) {
+      for (int i = lane * 8; i < W; i += 256) {
+        const uint4 p = *reinterpret_cast<const uint4*>(wr + i);
+        const float* h = row + i;
+        acc = fmaf(h[0], lo2f(p.x), acc), acc = fmaf(h[1], hi2f(p.x), acc), acc = fmaf(h[2], lo2f(p.y), acc), acc = fmaf(h[3], hi2f(p.y), acc);
+        acc = fmaf(h[4], lo2f(p.z), acc), acc = fmaf(h[5], hi2f(p.z), acc), acc = fmaf(h[6], lo2f(p.w), acc), acc = fmaf(h[7], hi2f(p.w), acc);
+      }
+    } else {
+      for (int i = lane; i < W; i += 32) acc = fmaf(row[i], bf2f(wr[i]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) zl[e] = acc;
+  }
+  __syncthreads();
+  if (warp == 0)
+    route_sigmoid_row(zl, zl + rt.experts, rt.experts, rt.top, rt.groups, rt.keep, rt.correction, rt.scale, rt.top_idx + (size_t)r * rt.top,
+                      rt.top_w + (size_t)r * rt.top, lane);
 }
 
 // one CTA per row.  The CTA of a segment's first row also moves the segment's last normed row into the carried row:
@@ -119,7 +148,14 @@ cudaError_t launch_rms_step(const RmsStep& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;
   const bool add = a.y || a.y_bf || a.mix.ye, read = a.h || a.h_bf;
   if ((add && (!a.w_out || a.gather)) || (read && !a.w_in) || (!add && !read)) return cudaErrorInvalidValue;
-  const size_t smem = (size_t)a.width * sizeof(float);
+  size_t smem = (size_t)a.width * sizeof(float);
+  if (a.route.w_router) {
+    const RouteRider& rt = a.route;
+    if (!read || a.gather || rt.experts <= 0 || rt.top <= 0 || rt.top > rt.experts || rt.groups <= 0 || rt.experts % rt.groups || rt.keep <= 0 ||
+        rt.keep > rt.groups || !rt.top_idx || !rt.top_w)
+      return cudaErrorInvalidValue;
+    smem += ((size_t)rt.experts + route_scratch_floats(rt.experts, rt.groups)) * sizeof(float);
+  }
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     cudaError_t r = cudaFuncSetAttribute(rms_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);

@@ -314,27 +314,33 @@ def test_bf16_prompt_attention_on_tensor_cores_keeps_the_edges(tmp_path):
     # projections wide enough for the tcgen05 GEMM and experts that take the grouped tensor-core GEMM (tiles wider than
     # the 32 gated columns and the 64 output columns).  The tolerance is bf16's; the fault it guards against is far larger.
     layers = [U.attn(heads=4, kv_heads=2, dim=24, vdim=20, window=37, scale=0.6, mlp=U.dense(ff=128)),
+              U.attn(heads=2, kv_heads=1, dim=32, vdim=16, window=0, scale=0.4, v_mix=False, mlp=None),  # no mask: tiles in pairs
+              # last, so that an expert chosen otherwise at bf16 precision (a close call) stays in its own row
               U.attn(heads=4, kv_heads=2, dim=16, vdim=20, window=70, scale=0.5, mlp=U.moe(experts=6, top=2, ff=32, shared_ff=64))]
     cfg = U.make_config(layers, width=64, vocab=29)
     w = U.random_weights(cfg, seed=31, gain=1.5)
-    U.set_values(w, "l0.shift", np.zeros(64))
-    U.set_values(w, "l1.shift", np.zeros(64))
+    for i in range(3):
+        U.set_values(w, f"l{i}.shift", np.zeros(64))
+    U.set_values(w, "l2.mlp.router", 4.0 * w["l2.mlp.router"][1])  # a decisive router: few close calls for bf16 to turn
     reqs = [_tokens(cfg, 150, 4), _tokens(cfg, 81, 5)]
     right = [_oracle_logits(cfg, w, t) for t in reqs]
-    tol = 3e-2
-    for size in (38, 36):
+    tol = 4e-2  # nine tenths of the rows; the median row stays under half of it through three bf16 layers
+
+    def rows(got, want):
+        return np.sqrt(((got - want) ** 2).mean(-1)) / np.sqrt((want ** 2).mean(-1))
+    for size in (38, 36):  # a window one key off moves the MEDIAN row four times further than the median may go
         bad = copy.deepcopy(cfg)
         bad["layers"][0]["mixer"]["mask"]["size"] = size
-        assert U.rel_err(_oracle_logits(bad, w, reqs[0])[40:], right[0][40:]) > 3 * tol, size
+        assert np.median(rows(_oracle_logits(bad, w, reqs[0]), right[0])[40:]) > 2 * tol, size
     eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=24, rows=256)
     a, b = eng.new_sequence(), eng.new_sequence()
     lg = eng.forward_batch([(a, reqs[0]), (b, reqs[1][:70])], range(220))
     lg2 = eng.forward_batch([(b, reqs[1][70:])], range(11))  # the per-row kernel over the same bf16 rows
     eng.close()
-    ea = np.sqrt(((lg[:150] - right[0]) ** 2).mean(-1)) / np.sqrt((right[0] ** 2).mean(-1))
-    eb = np.sqrt(((np.concatenate([lg[150:], lg2]) - right[1]) ** 2).mean(-1)) / np.sqrt((right[1] ** 2).mean(-1))
-    assert np.median(ea) < tol / 3 and np.quantile(ea, 0.95) < tol, (np.median(ea), ea.max())
-    assert np.median(eb) < tol / 3 and np.quantile(eb, 0.95) < tol, (np.median(eb), eb.max())
+    ea = rows(lg[:150], right[0])
+    eb = rows(np.concatenate([lg[150:], lg2]), right[1])
+    assert np.median(ea) < tol / 2 and np.quantile(ea, 0.9) < tol, (np.median(ea), ea.max())
+    assert np.median(eb) < tol / 2 and np.quantile(eb, 0.9) < tol, (np.median(eb), eb.max())
 
 
 def test_bf16_other_sizes_and_wide_key_rows(tmp_path):
