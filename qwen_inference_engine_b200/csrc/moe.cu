@@ -127,6 +127,73 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* top_idx, int
   }
 }
 
+// The same grouping for many assignments: the 32 warps of one CTA each take a contiguous chunk; a step of 32 assignments
+// finds, with one match, every lane's rank among the lanes of its expert.  Pass 1 counts per (warp, expert), a scan over
+// (expert, warp) gives every warp its first slot per expert, pass 2 hands out the slots: ascending assignment order within
+// an expert, exactly as the kernel above.  Shared memory: base [32][experts] ints.
+__global__ void __launch_bounds__(1024) moe_group_chunked_kernel(const int* __restrict__ top_idx, int n_assign, int top, int experts,
+                                                                 int* __restrict__ grp_off, int* __restrict__ perm_row, int* __restrict__ slot_of) {
+  extern __shared__ int base[];  // [32][experts]
+  pdl_wait();
+  pdl_trigger();
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = ((n_assign + 31) / 32 + 31) / 32 * 32;  // per warp, a multiple of 32
+  const int i0 = w * chunk, i1 = min(n_assign, i0 + chunk);
+  int* mine = base + w * experts;
+  for (int e = lane; e < experts; e += 32) mine[e] = 0;
+  __syncwarp();
+  for (int s = i0; s < i1; s += 32) {
+    const int i = s + lane;
+    const bool on = i < i1;
+    const int e = on ? top_idx[i] : -1 - lane;  // idle lanes match nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (on && (peers & ((1u << lane) - 1u)) == 0) mine[e] += __popc(peers);  // the first lane of each expert adds its count
+    __syncwarp();
+  }
+  __syncthreads();
+  // first slot of (expert, warp): experts in order, within an expert the warps in order
+  if (w == 0) {
+    int run = 0;
+    for (int e0 = 0; e0 < experts; e0 += 32) {
+      const int e = e0 + lane;
+      int tot = 0;
+      if (e < experts)
+        for (int ww = 0; ww < 32; ++ww) tot += base[ww * experts + e];
+      int inc = tot;  // inclusive scan over the 32 experts of this step
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+      }
+      int first = run + inc - tot;
+      if (e < experts) {
+        grp_off[e] = first;
+        for (int ww = 0; ww < 32; ++ww) {
+          const int c = base[ww * experts + e];
+          base[ww * experts + e] = first;
+          first += c;
+        }
+      }
+      run += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) grp_off[experts] = run;
+  }
+  __syncthreads();
+  for (int s = i0; s < i1; s += 32) {
+    const int i = s + lane;
+    const bool on = i < i1;
+    const int e = on ? top_idx[i] : -1 - lane;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (on) {
+      const int slot = mine[e] + __popc(peers & ((1u << lane) - 1u));
+      perm_row[slot] = i / top;
+      slot_of[i] = slot;
+    }
+    __syncwarp();
+    if (on && (peers & ((1u << lane) - 1u)) == 0) mine[e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ ye, const int* __restrict__ slot_of, const float* __restrict__ top_w, int top,
                                    const float* __restrict__ ys, const float* __restrict__ z, int ldz, int gate_col, float* __restrict__ y,
                                    int width) {
@@ -168,6 +235,14 @@ cudaError_t launch_moe_route_sigmoid(const float* z, int ldz, int experts, int t
 
 cudaError_t launch_moe_group(const int* top_idx, int n_assign, int top, int experts, int* grp_off, int* perm_row, int* slot_of, cudaStream_t st) {
   if (n_assign <= 0) return cudaSuccess;
+  if (n_assign >= 1024 && experts <= 1024) {  // many assignments: chunks over the warps instead of a warp per expert over all of them
+    const size_t smem = (size_t)32 * experts * sizeof(int);
+    if (smem > 48 * 1024) {
+      cudaError_t r = cudaFuncSetAttribute(moe_group_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+      if (r != cudaSuccess) return r;
+    }
+    return launch_k(moe_group_chunked_kernel, dim3(1), dim3(1024), smem, st, top_idx, n_assign, top, experts, grp_off, perm_row, slot_of);
+  }
   int threads = 32 * experts;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   const size_t bytes = (size_t)n_assign * sizeof(int);
