@@ -467,9 +467,9 @@ def ditenex_config(z, vocab=32000):
     mx = {"dim": 64, "heads": W // 128, "kv_heads": 2, "mask": {"size": z["window"]}, "scale": 0.125, "v_mix": True, "vdim": 128}
     dense = {"ff": 3 * (z["top"] * z["ff"] + z["sff"]) // 2, "kind": "dense"}
     moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "shared": {"ff": z["sff"]},
-           "router": {"experts": z["experts"], "groups": {"count": 4, "keep": 2}, "scale": 1.5, "top": z["top"]}}
+           "router": {"experts": z["experts"], "groups": {"count": 4, "keep": 2}, "scale": 2.0, "top": z["top"]}}
     layers = [{"type": "attention", "mixer": mx, "mlp": m} for m in (dense, moe, dense, moe)]
-    return {"architecture": "Ditenex", "layers": layers, "max_positions": 8192, "norm": {"eps": 1e-6}, "residual_mult": 0.3, "vocab": vocab, "width": W}
+    return {"architecture": "Ditenex", "layers": layers, "max_positions": 8192, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "vocab": vocab, "width": W}
 
 
 def ditenex_macs_per_token(cfg):

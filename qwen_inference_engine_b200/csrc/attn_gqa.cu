@@ -611,28 +611,9 @@ __global__ void __launch_bounds__(128) gqa_finish_kernel(const GqaAttnArgs a, in
   for (int c = threadIdx.x; c < vd; c += blockDim.x) out[c] = o[c] * rstd;
 }
 
-__global__ void __launch_bounds__(256) talk_queries_kernel(const TalkQueries t) {
-  extern __shared__ float tq_smem[];
-  pdl_wait();
-  pdl_trigger();
-  talk_queries_row(t, blockIdx.x, tq_smem);
-}
-
 }  // namespace
 
 static size_t talk_smem(const TalkQueries& t) { return ((size_t)t.heads * t.dim + (size_t)t.heads * t.heads) * sizeof(float); }
-
-cudaError_t launch_talk_queries(const TalkQueries& t, int n, cudaStream_t st) {
-  if (n <= 0) return cudaSuccess;
-  if (!t.talk || t.heads <= 0 || t.kv_heads <= 0 || t.heads % t.kv_heads) return cudaErrorInvalidValue;
-  const size_t smem = talk_smem(t);
-  if (smem > 48 * 1024) {
-    if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    cudaError_t r = cudaFuncSetAttribute(talk_queries_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (r != cudaSuccess) return r;
-  }
-  return launch_k(talk_queries_kernel, dim3(n), dim3(256), smem, st, t);
-}
 
 cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;

@@ -8,7 +8,7 @@
 // embedding table.  Residual stream, norms, softmax, router and the carried rows are fp32.
 //
 // The mechanisms are launchers with their constants as arguments so that another design can use them: the norms and
-// the token shift (rmsnorm_f32.cu), the activations (activations.cu), the router (moe.cu), the query mixing, distance
+// the token shift (rmsnorm_f32.cu), the activations (activations.cu), the router (moe_route.cuh), the query mixing, distance
 // slopes, shared keys and elementwise gate of the paged attention (attn_gqa.cu, fosavik.h).  ditenex_model.cu holds the
 // configuration reader, the weight loader and the launch order.  The family shares the engine's sequences, page
 // allocator, block tables, row metadata, sampler, scheduler and C ABI with the other families (engine.h, family.h).
@@ -33,7 +33,10 @@ namespace qie {
 //                                        of the row, computed on the fly from `mix`; mix.z == null: shared expert ungated)
 //   read (h != null):                    h[r] = rms(x[src(r)]) w_in,  src(r) = gather ? gather[r] : r
 // Rider of the read half in front of a mixture of experts: the row's router logits z_e = w_router[e, :] . h (fp32, from the
-// normed row while it is in shared memory) and the choice of launch_moe_route_sigmoid below, by the same CTA.
+// normed row while it is in shared memory) and the choice (moe_route.cuh), by the same CTA:
+// s = sigmoid(z); choice score c = s + correction.  The experts form `groups` equal runs of neighbours; a group's score is
+// the sum of its two largest c; only experts of the `keep` best groups can be chosen; the `top` largest c among them
+// (lowest index first among equals) are chosen with weights s * scale (not renormalised).
 struct RouteRider {
   const bf16* w_router = nullptr;  // [experts, width]; null: no rider
   const bf16* correction = nullptr;
@@ -89,13 +92,6 @@ cudaError_t launch_xielu_bf16(bf16* z, int ld, int cols, const bf16* pq, int n, 
 cudaError_t launch_silu_glu(const float* gu, int ld, float* out, int ldo, int ff, int n, cudaStream_t st);
 cudaError_t launch_silu_glu_bf16(const bf16* gu, int ld, bf16* out, int ldo, int ff, int n, cudaStream_t st);
 
-// ---------------------------------------------------------------- sigmoid router with group-limited choice (moe.cu)
-// s = sigmoid(z[r, 0:experts]); choice score c = s + correction.  The experts form `groups` equal runs of neighbours; a
-// group's score is the sum of its two largest c; only experts of the `keep` best groups can be chosen; the `top`
-// largest c among them (lowest index first among equals) are chosen with weights s * scale (not renormalised).
-cudaError_t launch_moe_route_sigmoid(const float* z, int ldz, int experts, int top, int groups, int keep, const bf16* correction, float scale,
-                                     int* top_idx, float* top_w, int n, cudaStream_t st);
-
 // ---------------------------------------------------------------- the model (ditenex_model.cu)
 struct DxLayer {
   int heads = 0, kv_heads = 0, dim = 0, vdim = 0, window = 0;
@@ -136,9 +132,9 @@ struct DxModel : RowFamily {
   float* carry = nullptr;
   size_t slot_floats = 0;
   // activations (fp32), sized by max_batch_tokens: x residual stream, hn normed sublayer input, y sublayer output,
-  // p0 projections / hidden rows, p1 attention output, p2 mixed queries, vf first-layer values, zr router,
+  // p0 projections / hidden rows, p1 attention output, p2 mixed queries, vf first-layer values, top_w / top_idx router choice,
   // he / hg / ye expert rows grouped by expert, hs / ys shared expert, xo normed output rows
-  float *x = nullptr, *hn = nullptr, *y = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *vf = nullptr, *zr = nullptr, *top_w = nullptr;
+  float *x = nullptr, *hn = nullptr, *y = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *vf = nullptr, *top_w = nullptr;
   float *he = nullptr, *hg = nullptr, *ye = nullptr, *hs = nullptr, *ys = nullptr, *xo = nullptr;
   int *top_idx = nullptr, *grp_off = nullptr, *perm_row = nullptr, *slot_of = nullptr;
   int vf_width = 0;

@@ -185,7 +185,7 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   e->cfg = qie_config{m->width, 0, (int)m->layers.size(), 0, 0, 0, m->vocab, context};
   size_t page_elems = 0, total_heads = 0;
   size_t w0 = 1, w1 = 1, w2 = 1, hmv = 1, maxk = m->width, maxn = m->width;
-  size_t w_zr = 1, w_top = 1, w_he = 1, w_hs = 1, w_ff = 1;
+  size_t w_top = 1, w_he = 1, w_hs = 1, w_ff = 1;
   int max_experts = 0;
   for (const DxLayer& L : m->layers) total_heads += L.heads;
   std::vector<float> slopes(total_heads);
@@ -229,7 +229,6 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
     } else {
       L.w_router = P(p + "mlp.router"), L.correction = P(p + "mlp.correction");
       L.w_egu = P(p + "mlp.e0.gate"), L.w_edown = P(p + "mlp.e0.down");
-      w_zr = std::max(w_zr, (size_t)L.experts);
       w_top = std::max(w_top, (size_t)L.top);
       w_he = std::max(w_he, (size_t)L.top * 2 * L.ff);
       max_experts = std::max(max_experts, L.experts);
@@ -266,7 +265,6 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   CUS(fbuf(&m->p1, R * w1));
   CUS(fbuf(&m->p2, R * w2));
   CUS(fbuf(&m->vf, R * std::max(m->vf_width, 1)));
-  CUS(fbuf(&m->zr, R * w_zr));
   CUS(fbuf(&m->top_w, R * w_top));
   CUS(fbuf(&m->he, R * w_he));
   CUS(fbuf(&m->hg, R * w_he / 2 + 1));
@@ -331,7 +329,7 @@ std::string ditenex_create_synthetic(qie_engine* e, const std::string& cfg_json,
 }
 
 void DxModel::release() {
-  void* dev[] = {blob, slopes_all, kv_pool, carry, x, hn, y, p0, p1, p2, vf, zr, top_w, he, hg, ye, hs, ys, xo, top_idx, perm_row, slot_of, grp_off, attn_ws,
+  void* dev[] = {blob, slopes_all, kv_pool, carry, x, hn, y, p0, p1, p2, vf, top_w, he, hg, ye, hs, ys, xo, top_idx, perm_row, slot_of, grp_off, attn_ws,
                  hb, ub, ub2, yb, ysb, hgb};
   tc.release();
   release_row_buffers();

@@ -142,8 +142,6 @@ struct GqaAttnArgs {
 // floats of workspace that n rows need with one split
 inline size_t gqa_ws_floats(int n, int heads, int maps, int vdim) { return (size_t)n * heads * maps * (vdim + 2); }
 cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_launches = nullptr);
-// the head-mixed queries alone (KvStoreArgs::tq does the same inside the store)
-cudaError_t launch_talk_queries(const TalkQueries& t, int n, cudaStream_t st);
 
 // ---------------------------------------------------------------- short convolution and recurrences (recurrent.cu)
 // Causal per-channel convolution over the rows of each segment: out[t, c] = act(b[c] + sum_i w[c, i] * in(t - (taps-1-i), c)),

@@ -3,9 +3,7 @@
 // (launch_gemm_f32 with grp_off / row_idx), and the weighted combine with an optional gated shared expert.
 // All of it fp32; a row's choice, weights and sums do not depend on the other rows of the launch (its slot in
 // the grouped buffers does, the values stored there do not).
-#include "ditenex.h"
 #include "launch.h"
-#include "moe_route.cuh"
 #include "nogatar.h"
 
 namespace qie {
@@ -65,19 +63,6 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int exper
     const float inv = 1.0f / (chosen_sum + 1e-20f);
     for (int k = 0; k < top; ++k) top_w[(size_t)r * top + k] *= inv;
   }
-}
-
-// Sigmoid router with a choice correction and group-limited top-k (ditenex.h, moe_route.cuh).  One warp per row.
-__global__ void moe_route_sigmoid_kernel(const float* __restrict__ z, int ldz, int experts, int top, int groups, int keep,
-                                         const bf16* __restrict__ correction, float scale, int* __restrict__ top_idx, float* __restrict__ top_w, int n) {
-  extern __shared__ float sc[];
-  pdl_wait();
-  pdl_trigger();
-  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = blockIdx.x * (blockDim.x >> 5) + w;
-  if (r >= n) return;
-  route_sigmoid_row(z + (size_t)r * ldz, sc + (size_t)w * route_scratch_floats(experts, groups), experts, top, groups, keep, correction, scale,
-                    top_idx + (size_t)r * top, top_w + (size_t)r * top, lane);
 }
 
 // one CTA; warp w serves experts w, w + nw, ...: an ordered compaction of the assignments that chose the expert
@@ -219,18 +204,6 @@ cudaError_t launch_moe_route(const float* z, int ldz, int experts, int top, int*
   if ((size_t)warps * experts * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
   return launch_k(moe_route_kernel, dim3((n + warps - 1) / warps), dim3(32 * warps), (size_t)warps * experts * sizeof(float), st, z, ldz, experts,
                   top, top_idx, top_w, n);
-}
-
-cudaError_t launch_moe_route_sigmoid(const float* z, int ldz, int experts, int top, int groups, int keep, const bf16* correction, float scale,
-                                     int* top_idx, float* top_w, int n, cudaStream_t st) {
-  if (n <= 0) return cudaSuccess;
-  if (experts <= 0 || top <= 0 || top > experts || groups <= 0 || experts % groups || keep <= 0 || keep > groups) return cudaErrorInvalidValue;
-  const size_t per_warp = route_scratch_floats(experts, groups) * sizeof(float);
-  int warps = 8;
-  while (warps > 1 && warps * per_warp > 40 * 1024) warps /= 2;
-  if (warps * per_warp > 48 * 1024) return cudaErrorInvalidValue;
-  return launch_k(moe_route_sigmoid_kernel, dim3((n + warps - 1) / warps), dim3(32 * warps), warps * per_warp, st, z, ldz, experts, top, groups,
-                  keep, correction, scale, top_idx, top_w, n);
 }
 
 cudaError_t launch_moe_group(const int* top_idx, int n_assign, int top, int experts, int* grp_off, int* perm_row, int* slot_of, cudaStream_t st) {

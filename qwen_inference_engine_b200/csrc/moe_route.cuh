@@ -1,5 +1,5 @@
 // moe_route.cuh -- the choice of a sigmoid router with a correction and group-limited top-k for ONE row, by one warp
-// (ditenex.h: launch_moe_route_sigmoid, and as a rider of the norm in front of a mixture of experts, rmsnorm_f32.cu).
+// (ditenex.h: RouteRider, the rider of the norm in front of a mixture of experts, rmsnorm_f32.cu).
 #pragma once
 #include "common.cuh"
 

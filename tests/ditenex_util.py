@@ -16,7 +16,7 @@ def dense(ff=14):
     return {"ff": ff, "kind": "dense"}
 
 
-def moe(experts=6, top=2, ff=9, groups=3, keep=2, scale=1.5, shared_ff=10):
+def moe(experts=6, top=2, ff=9, groups=3, keep=2, scale=1.25, shared_ff=10):
     m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "scale": scale, "top": top}}
     if groups:
         m["router"]["groups"] = {"count": groups, "keep": keep}
