@@ -481,6 +481,14 @@ __global__ void rows_bf16_to_f32_kernel(const bf16* __restrict__ in, int cols, f
   pdl_trigger();
   const bf16* src = in + (size_t)blockIdx.x * cols;
   float* dst = out + (size_t)blockIdx.x * ld_out;
+  if (act == 0 && cols % 8 == 0 && ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 8) {  // 8 elements per 16-byte load
+      const uint4 p = *reinterpret_cast<const uint4*>(src + i);
+      *reinterpret_cast<float4*>(dst + i) = make_float4(lo2f(p.x), hi2f(p.x), lo2f(p.y), hi2f(p.y));
+      *reinterpret_cast<float4*>(dst + i + 4) = make_float4(lo2f(p.z), hi2f(p.z), lo2f(p.w), hi2f(p.w));
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < cols; i += blockDim.x) {
     float v = bf2f(src[i]);
     if (act == 1) {

@@ -20,12 +20,53 @@ __device__ __forceinline__ float block_sum_r(float v, float* red) {
   return t;
 }
 
+// V consecutive elements per thread and step (V = 4: 16-byte fp32 and 8-byte bf16 accesses when the width and the
+// pointers allow it; V = 1 otherwise)
+template <int V>
+struct Pack {
+  float v[V];
+};
+template <int V>
+__device__ __forceinline__ Pack<V> ld_f32(const float* p) {
+  Pack<V> r;
+  if constexpr (V == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    r.v[0] = t.x, r.v[1] = t.y, r.v[2] = t.z, r.v[3] = t.w;
+  } else {
+    r.v[0] = p[0];
+  }
+  return r;
+}
+template <int V>
+__device__ __forceinline__ Pack<V> ld_bf16(const bf16* p) {
+  Pack<V> r;
+  if constexpr (V == 4) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    r.v[0] = lo2f(t.x), r.v[1] = hi2f(t.x), r.v[2] = lo2f(t.y), r.v[3] = hi2f(t.y);
+  } else {
+    r.v[0] = bf2f(p[0]);
+  }
+  return r;
+}
+template <int V>
+__device__ __forceinline__ void st_f32(float* p, const Pack<V>& r) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  else p[0] = r.v[0];
+}
+template <int V>
+__device__ __forceinline__ void st_bf16(bf16* p, const Pack<V>& r) {
+  if constexpr (V == 4) *reinterpret_cast<uint2*>(p) = make_uint2(pack2(f2bf(r.v[0]), f2bf(r.v[1])), pack2(f2bf(r.v[2]), f2bf(r.v[3])));
+  else p[0] = f2bf(r.v[0]);
+}
+
+template <int V>
 __global__ void __launch_bounds__(256) rms_step_kernel(const RmsStep a) {
-  extern __shared__ float row[];  // [width]
+  extern __shared__ __align__(16) float row[];  // [width]
   __shared__ float red[32];
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x, W = a.width;
+  const int t0 = threadIdx.x * V, step = blockDim.x * V;
   const bool add = a.y || a.y_bf || a.mix.ye;
   const int src = a.gather ? a.gather[r] : r;  // the add half is never combined with a gather
   float* xr = a.x + (size_t)src * W;
@@ -33,46 +74,66 @@ __global__ void __launch_bounds__(256) rms_step_kernel(const RmsStep a) {
   if (add) {
     float s = 0.f;
     if (a.y || a.y_bf) {
-      const float* y = a.y + (size_t)r * W;
-      const bf16* yb = a.y_bf + (size_t)r * W;
-      for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float v = a.y_bf ? bf2f(yb[i]) : y[i];
-        row[i] = v;
-        s = fmaf(v, v, s);
+      for (int i = t0; i < W; i += step) {
+        const Pack<V> p = a.y_bf ? ld_bf16<V>(a.y_bf + (size_t)r * W + i) : ld_f32<V>(a.y + (size_t)r * W + i);
+        st_f32<V>(row + i, p);
+#pragma unroll
+        for (int u = 0; u < V; ++u) s = fmaf(p.v[u], p.v[u], s);
       }
     } else {  // the chosen experts' outputs of this row, weighted, plus the shared expert (gated only when mix.z is given)
       const MoeMix& m = a.mix;
       const bool shared = m.ys || a.ys_bf;
       const float sg = shared ? (m.z ? 1.0f / (1.0f + expf(-m.z[(size_t)r * m.ldz + m.gate_col])) : 1.0f) : 0.f;
-      for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float v = 0.f;
-        for (int k = 0; k < m.top; ++k) v = fmaf(m.top_w[(size_t)r * m.top + k], m.ye[(size_t)m.slot_of[(size_t)r * m.top + k] * W + i], v);
-        if (shared) v = fmaf(sg, a.ys_bf ? bf2f(a.ys_bf[(size_t)r * W + i]) : m.ys[(size_t)r * W + i], v);
-        row[i] = v;
-        s = fmaf(v, v, s);
+      for (int i = t0; i < W; i += step) {
+        Pack<V> p;
+#pragma unroll
+        for (int u = 0; u < V; ++u) p.v[u] = 0.f;
+        for (int k = 0; k < m.top; ++k) {
+          const float wk = m.top_w[(size_t)r * m.top + k];
+          const Pack<V> e = ld_f32<V>(m.ye + (size_t)m.slot_of[(size_t)r * m.top + k] * W + i);
+#pragma unroll
+          for (int u = 0; u < V; ++u) p.v[u] = fmaf(wk, e.v[u], p.v[u]);
+        }
+        if (shared) {
+          const Pack<V> e = a.ys_bf ? ld_bf16<V>(a.ys_bf + (size_t)r * W + i) : ld_f32<V>(m.ys + (size_t)r * W + i);
+#pragma unroll
+          for (int u = 0; u < V; ++u) p.v[u] = fmaf(sg, e.v[u], p.v[u]);
+        }
+        st_f32<V>(row + i, p);
+#pragma unroll
+        for (int u = 0; u < V; ++u) s = fmaf(p.v[u], p.v[u], s);
       }
     }
     const float rstd = 1.0f / sqrtf(block_sum_r(s, red) / (float)W + a.eps);
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      const float v = xr[i] + a.mult * (row[i] * rstd * bf2f(a.w_out[i]));
-      xr[i] = v;
-      row[i] = v;
-      sq = fmaf(v, v, sq);
+    for (int i = t0; i < W; i += step) {
+      const Pack<V> y = ld_f32<V>(row + i), x = ld_f32<V>(xr + i), w = ld_bf16<V>(a.w_out + i);
+      Pack<V> o;
+#pragma unroll
+      for (int u = 0; u < V; ++u) {
+        o.v[u] = x.v[u] + a.mult * (y.v[u] * rstd * w.v[u]);
+        sq = fmaf(o.v[u], o.v[u], sq);
+      }
+      st_f32<V>(xr + i, o);
+      st_f32<V>(row + i, o);
     }
   } else if (a.h || a.h_bf) {
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      const float v = xr[i];
-      row[i] = v;
-      sq = fmaf(v, v, sq);
+    for (int i = t0; i < W; i += step) {
+      const Pack<V> x = ld_f32<V>(xr + i);
+      st_f32<V>(row + i, x);
+#pragma unroll
+      for (int u = 0; u < V; ++u) sq = fmaf(x.v[u], x.v[u], sq);
     }
   }
   if (!a.h && !a.h_bf) return;
   const float rstd = 1.0f / sqrtf(block_sum_r(sq, red) / (float)W + a.eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = row[i] * rstd * bf2f(a.w_in[i]);
-    if (a.h) a.h[(size_t)r * W + i] = v;
-    if (a.h_bf) a.h_bf[(size_t)r * W + i] = f2bf(v);
-    row[i] = v;
+  for (int i = t0; i < W; i += step) {
+    const Pack<V> x = ld_f32<V>(row + i), w = ld_bf16<V>(a.w_in + i);
+    Pack<V> o;
+#pragma unroll
+    for (int u = 0; u < V; ++u) o.v[u] = x.v[u] * rstd * w.v[u];
+    if (a.h) st_f32<V>(a.h + (size_t)r * W + i, o);
+    if (a.h_bf) st_bf16<V>(a.h_bf + (size_t)r * W + i, o);
+    st_f32<V>(row + i, o);
   }
   if (!a.route.w_router) return;
   // router logits of the row: a warp per expert, lanes stride the width (16-byte weight loads when the rows allow it)
@@ -105,11 +166,13 @@ __global__ void __launch_bounds__(256) rms_step_kernel(const RmsStep a) {
 
 // one CTA per row.  The CTA of a segment's first row also moves the segment's last normed row into the carried row:
 // each thread reads the old carried elements it needs before it overwrites exactly those, and no other CTA touches them.
+template <int V>
 __global__ void __launch_bounds__(256) rms_shift_kernel(const RmsShiftArgs a) {
   __shared__ float red[32];
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x, W = a.width;
+  const int t0 = threadIdx.x * V, step = blockDim.x * V;
   // the segment of this row: the last s with seg_start[s] <= r
   int lo = 0, hi = a.n_seg - 1;
   while (lo < hi) {
@@ -122,23 +185,28 @@ __global__ void __launch_bounds__(256) rms_shift_kernel(const RmsShiftArgs a) {
   const float* xr = a.x + (size_t)r * W;
   const float* xp = head ? a.x + (size_t)last * W : xr - W;  // the other row this CTA norms: the one before, or (first row) the segment's last
   float s0 = 0.f, s1 = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = xr[i], u = xp[i];
-    s0 = fmaf(v, v, s0);
-    s1 = fmaf(u, u, s1);
+  for (int i = t0; i < W; i += step) {
+    const Pack<V> v = ld_f32<V>(xr + i), u = ld_f32<V>(xp + i);
+#pragma unroll
+    for (int k = 0; k < V; ++k) s0 = fmaf(v.v[k], v.v[k], s0), s1 = fmaf(u.v[k], u.v[k], s1);
   }
   const float r0 = 1.0f / sqrtf(block_sum_r(s0, red) / (float)W + a.eps);
   const float r1 = 1.0f / sqrtf(block_sum_r(s1, red) / (float)W + a.eps);
   float* carry = a.carry + (size_t)a.seg_slot[lo] * a.slot_stride;
-  float* out = a.out + (size_t)r * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float w = bf2f(a.w[i]);
-    const float h = xr[i] * r0 * w, o = xp[i] * r1 * w;
-    const float before = head ? carry[i] : o;
-    const float v = h + (before - h) * bf2f(a.mu[i]);
-    if (a.out) out[i] = v;
-    if (a.out_bf) a.out_bf[(size_t)r * W + i] = f2bf(v);
-    if (head) carry[i] = o;
+  for (int i = t0; i < W; i += step) {
+    const Pack<V> v = ld_f32<V>(xr + i), u = ld_f32<V>(xp + i), w = ld_bf16<V>(a.w + i), mu = ld_bf16<V>(a.mu + i);
+    Pack<V> before, o, res;
+    if (head) before = ld_f32<V>(carry + i);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float h = v.v[k] * r0 * w.v[k];
+      o.v[k] = u.v[k] * r1 * w.v[k];
+      const float b = head ? before.v[k] : o.v[k];
+      res.v[k] = h + (b - h) * mu.v[k];
+    }
+    if (a.out) st_f32<V>(a.out + (size_t)r * W + i, res);
+    if (a.out_bf) st_bf16<V>(a.out_bf + (size_t)r * W + i, res);
+    if (head) st_f32<V>(carry + i, o);
   }
 }
 
@@ -156,18 +224,26 @@ cudaError_t launch_rms_step(const RmsStep& a, cudaStream_t st) {
       return cudaErrorInvalidValue;
     smem += ((size_t)rt.experts + route_scratch_floats(rt.experts, rt.groups)) * sizeof(float);
   }
+  // 16-byte accesses when every row starts on a 16-byte boundary (cudaMalloc'd buffers, width a multiple of 4)
+  auto al = [](const void* p, size_t b) { return (reinterpret_cast<uintptr_t>(p) & (b - 1)) == 0; };
+  const bool vec = a.width % 4 == 0 && al(a.x, 16) && al(a.y, 16) && al(a.y_bf, 8) && al(a.ys_bf, 8) && al(a.mix.ye, 16) && al(a.mix.ys, 16) &&
+                   al(a.h, 16) && al(a.h_bf, 8) && al(a.w_out, 8) && al(a.w_in, 8);
+  auto* kern = vec ? rms_step_kernel<4> : rms_step_kernel<1>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    cudaError_t r = cudaFuncSetAttribute(rms_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t r = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (r != cudaSuccess) return r;
   }
-  return launch_k(rms_step_kernel, dim3(a.n), dim3(256), smem, st, a);
+  return launch_k(kern, dim3(a.n), dim3(256), smem, st, a);
 }
 
 cudaError_t launch_rms_shift(const RmsShiftArgs& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;
   if (a.n_seg <= 0 || !a.seg_start || !a.seg_slot || !a.carry) return cudaErrorInvalidValue;
-  return launch_k(rms_shift_kernel, dim3(a.n), dim3(256), 0, st, a);
+  auto al = [](const void* p, size_t b) { return (reinterpret_cast<uintptr_t>(p) & (b - 1)) == 0; };
+  const bool vec = a.width % 4 == 0 && a.slot_stride % 4 == 0 && al(a.x, 16) && al(a.out, 16) && al(a.out_bf, 8) && al(a.carry, 16) && al(a.w, 8) &&
+                   al(a.mu, 8);
+  return vec ? launch_k(rms_shift_kernel<4>, dim3(a.n), dim3(256), 0, st, a) : launch_k(rms_shift_kernel<1>, dim3(a.n), dim3(256), 0, st, a);
 }
 
 }  // namespace qie
