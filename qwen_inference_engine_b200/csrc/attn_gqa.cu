@@ -46,6 +46,29 @@ __device__ __forceinline__ void talk_queries_row(const TalkQueries& t, int r, fl
   }
 }
 
+// One group of d consecutive elements, by one warp: unit RMS norm times w (w null: as it is), then the rotation of the
+// first rope.dims elements by position p.  get(i) reads element i (bias added), put(i, x) writes it; every element is read
+// before the warp's reduction and written after it, by the lane that read it (or its pair), so put may overwrite get's source.
+template <typename Get, typename Put>
+__device__ __forceinline__ void norm_rope_group(const KvStoreArgs& a, int p, int lane, int d, Get get, const bf16* w, Put put) {
+  float rstd = 1.f;
+  if (w) {
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) s = fmaf(get(i), get(i), s);
+    rstd = 1.0f / sqrtf(warp_sum(s) / (float)d + a.eps);
+  }
+  auto val = [&](int i) { return w ? get(i) * rstd * bf2f(w[i]) : get(i); };
+  const int dims = a.rope.dims, half = dims / 2;
+  const int st1 = a.rope.half_layout ? 1 : 2, off2 = a.rope.half_layout ? half : 1;
+  for (int i = lane; i < half; i += 32) {
+    const float cs = a.rope.cos_t[(size_t)p * half + i], sn = a.rope.sin_t[(size_t)p * half + i];
+    const float u = val(st1 * i), v = val(st1 * i + off2);
+    put(st1 * i, u * cs - v * sn);
+    put(st1 * i + off2, v * cs + u * sn);
+  }
+  for (int i = dims + lane; i < d; i += 32) put(i, val(i));
+}
+
 // one CTA per row, one warp per normed group
 __global__ void __launch_bounds__(128) kv_store_rows_kernel(const KvStoreArgs a) {
   extern __shared__ float tq_smem[];  // only with the query rider
@@ -58,14 +81,10 @@ __global__ void __launch_bounds__(128) kv_store_rows_kernel(const KvStoreArgs a)
     char* row = const_cast<char*>(kv_row_ptr(a.c, a.block_table, a.max_pages, a.slot[r], a.pos[r]));
     const float* k = a.k + (size_t)r * a.ldk;
     auto key = [&](int i) { return a.k_bias ? k[i] + bf2f(a.k_bias[i]) : k[i]; };
-    if (a.k_norm) {
+    if (a.k_norm || a.rope.dims > 0) {
       const int d = a.norm_dim;
-      for (int g = warp; g < a.c.kw / d; g += nw) {
-        float s = 0.f;
-        for (int i = lane; i < d; i += 32) s = fmaf(key(g * d + i), key(g * d + i), s);
-        const float rstd = 1.0f / sqrtf(warp_sum(s) / (float)d + a.eps);
-        for (int i = lane; i < d; i += 32) store_elt(a.c, row, g * d + i, key(g * d + i) * rstd * bf2f(a.k_norm[i]));
-      }
+      for (int g = warp; g < a.c.kw / d; g += nw) norm_rope_group(a, a.pos[r], lane, d, [&](int i) { return key(g * d + i); }, a.k_norm,
+                                                                  [&](int i, float x) { store_elt(a.c, row, g * d + i, x); });
     } else {
       for (int i = threadIdx.x; i < a.c.kw; i += blockDim.x) store_elt(a.c, row, i, key(i));
     }
@@ -79,15 +98,12 @@ __global__ void __launch_bounds__(128) kv_store_rows_kernel(const KvStoreArgs a)
       store_elt(a.c, row, a.c.kw + i, x);
     }
   }
-  if (a.q && a.q_norm) {
+  if (a.q && (a.q_norm || a.rope.dims > 0 || a.q_bias)) {
     float* q = a.q + (size_t)r * a.ldq;
     const int d = a.norm_dim;
-    for (int h = warp; h < a.q_heads; h += nw) {
-      float s = 0.f;
-      for (int i = lane; i < d; i += 32) s = fmaf(q[h * d + i], q[h * d + i], s);
-      const float rstd = 1.0f / sqrtf(warp_sum(s) / (float)d + a.eps);
-      for (int i = lane; i < d; i += 32) q[h * d + i] = q[h * d + i] * rstd * bf2f(a.q_norm[i]);
-    }
+    for (int h = warp; h < a.q_heads; h += nw)
+      norm_rope_group(a, a.pos[r], lane, d, [&](int i) { return a.q_bias ? q[h * d + i] + bf2f(a.q_bias[h * d + i]) : q[h * d + i]; }, a.q_norm,
+                      [&](int i, float x) { q[h * d + i] = x; });
   }
 }
 
@@ -187,6 +203,7 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
         const float* kp = Kt + key * (kd + 1) + (qv % maps) * dim;
         s = 0.f;
         for (int c = 0; c < dim; ++c) s = fmaf(qp[c], kp[c], s);
+        if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
         if (a.slopes) s -= a.slopes[h0 + qv / maps] * (float)dist[key];
       }
       sc[i] = s;
@@ -297,6 +314,10 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
   const int pmax = pos0 + nrows - 1;
   const int lo_min = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
   const float slope = a.slopes ? a.slopes[h] : 0.f;
+  // soft cap of a scaled score: cap * tanh(s / cap) as cap * (1 - 2 / (exp(2 s / cap) + 1)); the weights become bf16 operands
+  // below, far coarser than the fast exponential
+  const float cap = a.softcap, cap2 = cap > 0.f ? 2.0f / cap : 0.f;
+  auto capped = [&](float v) { return cap > 0.f ? cap - 2.0f * cap / (__expf(fminf(v * cap2, 80.f)) + 1.0f) : v; };
   const int qr = lane >> 2, qc = (lane & 3) * 2;      // this thread's rows qr, qr + 8 and column pair of every 8-block
   const int wrow = warp * 16;
   const bool rv0 = wrow + qr < nrows, rv1 = wrow + qr + 8 < nrows;
@@ -402,7 +423,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
         for (int nb = 0; nb < PT_KEYS / 8; ++nb)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            s[nb][e] = fmaf(s[nb][e], a.scale, fmaf(slope, (float)(nb * 8 + (e & 1)), (e >> 1) ? d1 : d0));
+            s[nb][e] = capped(s[nb][e] * a.scale) + fmaf(slope, (float)(nb * 8 + (e & 1)), (e >> 1) ? d1 : d0);
             if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
             else mx0 = fmaxf(mx0, s[nb][e]);
           }
@@ -414,7 +435,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
             const int j = j0 + nb * 8 + qc + (e & 1);
             const int i = (e >> 1) ? i1 : i0;
             const bool ok = j <= i && (a.window <= 0 || i - j < a.window || j < a.keep_first);
-            s[nb][e] = ok ? s[nb][e] * a.scale - slope * (float)(i - j) : -INFINITY;  // the scale meets the fp32 score, not the bf16 operand
+            s[nb][e] = ok ? capped(s[nb][e] * a.scale) - slope * (float)(i - j) : -INFINITY;  // the scale meets the fp32 score, not the bf16 operand
             if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
             else mx0 = fmaxf(mx0, s[nb][e]);
           }
@@ -617,7 +638,7 @@ static size_t talk_smem(const TalkQueries& t) { return ((size_t)t.heads * t.dim 
 
 cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;
-  if (a.k_norm && (a.norm_dim <= 0 || a.c.kw % a.norm_dim)) return cudaErrorInvalidValue;
+  if ((a.k_norm || a.rope.dims > 0) && (a.norm_dim <= 0 || a.c.kw % a.norm_dim || a.rope.dims > a.norm_dim || a.rope.dims % 2)) return cudaErrorInvalidValue;
   size_t smem = 0;
   if (a.tq.talk) {
     if (a.tq.heads <= 0 || a.tq.kv_heads <= 0 || a.tq.heads % a.tq.kv_heads) return cudaErrorInvalidValue;

@@ -37,6 +37,10 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// the output gate of (row, head): sigmoid of the gate's pre-activation, 1 without a gate
+__device__ __forceinline__ float head_gate(const HeadGate& g, int r, int h) {
+  return g.z ? 1.0f / (1.0f + expf(-(g.z[(size_t)r * g.ld + h] + (g.bias ? bf2f(g.bias[h]) : 0.f)))) : 1.0f;
+}
 __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
@@ -52,7 +56,7 @@ __device__ __forceinline__ T* cache_row(const LatentCache& c, const int* block_t
 template <typename T>
 __global__ void latent_store_kernel(const LatentCache c, const float* __restrict__ dkv, int ld, const bf16* __restrict__ w_norm, float eps,
                                     const RopeTable rope, const int* __restrict__ pos, const int* __restrict__ slot,
-                                    const int* __restrict__ block_table, int max_pages, const QueryRope qr) {
+                                    const int* __restrict__ block_table, int max_pages, const QueryRope qr, const RowNorm qn) {
   __shared__ float red[4];
   pdl_wait();
   pdl_trigger();
@@ -68,11 +72,13 @@ __global__ void latent_store_kernel(const LatentCache c, const float* __restrict
   const float rinv = 1.0f / sqrtf(tot / (float)c.rank + eps);
   for (int i = threadIdx.x; i < c.rank; i += blockDim.x) st_elt<T>(dst + i, src[i] * rinv * bf2f(w_norm[i]));
   const int half = rope.dims / 2;
+  // the two members of rotated pair i: neighbours, or half the rotated dimensions apart
+  const int st1 = rope.half_layout ? 1 : 2, off2 = rope.half_layout ? half : 1;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float cs = rope.cos_t[(size_t)p * half + i], sn = rope.sin_t[(size_t)p * half + i];
-    const float u = src[c.rank + 2 * i], v = src[c.rank + 2 * i + 1];
-    st_elt<T>(dst + c.rank + 2 * i, u * cs - v * sn);
-    st_elt<T>(dst + c.rank + 2 * i + 1, v * cs + u * sn);
+    const float u = src[c.rank + st1 * i], v = src[c.rank + st1 * i + off2];
+    st_elt<T>(dst + c.rank + st1 * i, u * cs - v * sn);
+    st_elt<T>(dst + c.rank + st1 * i + off2, v * cs + u * sn);
   }
   for (int i = rope.dims + threadIdx.x; i < c.rot; i += blockDim.x) st_elt<T>(dst + c.rank + i, src[c.rank + i]);
   // the same rotation on the rotated part of every query head of the row (saves a launch per layer)
@@ -82,14 +88,30 @@ __global__ void latent_store_kernel(const LatentCache c, const float* __restrict
       const float* qs = qr.src + (size_t)r * qr.ld_src + (size_t)h * qr.hs_src;
       float* qd = qr.dst + (size_t)r * qr.ld_dst + (size_t)h * qr.hs_dst;
       const float cs = rope.cos_t[(size_t)p * half + j], sn = rope.sin_t[(size_t)p * half + j];
-      const float u = qs[2 * j], v = qs[2 * j + 1];
-      qd[2 * j] = u * cs - v * sn;
-      qd[2 * j + 1] = v * cs + u * sn;
+      const float u = qs[st1 * j], v = qs[st1 * j + off2];
+      qd[st1 * j] = u * cs - v * sn;
+      qd[st1 * j + off2] = v * cs + u * sn;
     }
     const int rest = c.rot - rope.dims;
     for (int i = threadIdx.x; i < qr.heads * rest; i += blockDim.x) {
       const int h = i / rest, j = rope.dims + i % rest;
       qr.dst[(size_t)r * qr.ld_dst + (size_t)h * qr.hs_dst + j] = qr.src[(size_t)r * qr.ld_src + (size_t)h * qr.hs_src + j];
+    }
+  }
+  // rider: a second vector of the row normed the same way (the query latent of a model whose queries pass a low-rank bottleneck)
+  if (qn.src) {
+    __syncthreads();  // red is read above
+    float t = 0.f;
+    const float* ql = qn.src + (size_t)r * qn.ld_src;
+    for (int i = threadIdx.x; i < qn.width; i += blockDim.x) t += ql[i] * ql[i];
+    t = warp_sum(t);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = t;
+    __syncthreads();
+    const float qinv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)qn.width + eps);
+    for (int i = threadIdx.x; i < qn.width; i += blockDim.x) {
+      const float v = ql[i] * qinv * bf2f(qn.w[i]);
+      if (qn.dst) qn.dst[(size_t)r * qn.ld_dst + i] = v;
+      if (qn.dst_bf) qn.dst_bf[(size_t)r * qn.ld_dst_bf + i] = f2bf(v);
     }
   }
 }
@@ -103,11 +125,12 @@ __global__ void rope_heads_kernel(const float* __restrict__ src, int ld_src, int
   const float* s = src + (size_t)r * ld_src + (size_t)h * hs_src;
   float* d = dst + (size_t)r * ld_dst + (size_t)h * hs_dst;
   const int half = rope.dims / 2;
+  const int st1 = rope.half_layout ? 1 : 2, off2 = rope.half_layout ? half : 1;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float cs = rope.cos_t[(size_t)p * half + i], sn = rope.sin_t[(size_t)p * half + i];
-    const float u = s[2 * i], v = s[2 * i + 1];
-    d[2 * i] = u * cs - v * sn;
-    d[2 * i + 1] = v * cs + u * sn;
+    const float u = s[st1 * i], v = s[st1 * i + off2];
+    d[st1 * i] = u * cs - v * sn;
+    d[st1 * i + off2] = v * cs + u * sn;
   }
   for (int i = rope.dims + threadIdx.x; i < rot; i += blockDim.x) d[i] = s[i];
 }
@@ -122,7 +145,7 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
                                                                 const bf16* __restrict__ sink, float scale, int window, int H_all, int HG, int TK,
                                                                 const int* __restrict__ pos, const int* __restrict__ slot,
                                                                 const int* __restrict__ block_table, int max_pages, int n_splits,
-                                                                float* __restrict__ ws) {
+                                                                float* __restrict__ ws, const HeadGate hg) {
   extern __shared__ float4 sm4[];
   float* sm = reinterpret_cast<float*>(sm4);
   pdl_wait();
@@ -226,7 +249,7 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
     __syncthreads();
   }
   if (n_splits <= 1) {
-    for (int i = tid; i < H * R; i += nt) out[((size_t)r * H_all + h0) * R + i] = s_acc[i] / s_l[i / R];
+    for (int i = tid; i < H * R; i += nt) out[((size_t)r * H_all + h0) * R + i] = s_acc[i] / s_l[i / R] * head_gate(hg, r, h0 + i / R);
     return;
   }
   // partial result of this split: [acc (R) | running maximum | running sum] per (row, head, split)
@@ -242,7 +265,7 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
 }
 
 // grid (rows, heads): out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M), splits in ascending order
-__global__ void latent_attention_combine_kernel(const float* __restrict__ ws, float* __restrict__ out, int H, int R, int n_splits) {
+__global__ void latent_attention_combine_kernel(const float* __restrict__ ws, float* __restrict__ out, int H, int R, int n_splits, const HeadGate hg) {
   pdl_wait();
   pdl_trigger();
   const float* w = ws + ((size_t)blockIdx.x * H + blockIdx.y) * n_splits * (R + 2);
@@ -259,7 +282,7 @@ __global__ void latent_attention_combine_kernel(const float* __restrict__ ws, fl
       const float ms = w[(size_t)s * (R + 2) + R];
       if (ms != -INFINITY) a = fmaf(w[(size_t)s * (R + 2) + d], expf(ms - M), a);
     }
-    out[((size_t)blockIdx.x * H + blockIdx.y) * R + d] = a / den;
+    out[((size_t)blockIdx.x * H + blockIdx.y) * R + d] = a / den * head_gate(hg, blockIdx.x, blockIdx.y);
   }
 }
 
@@ -287,7 +310,7 @@ template <int NBW>
 __global__ void __launch_bounds__(256) latent_attention_mma_kernel(const LatentCache c, const float* __restrict__ qa, float* __restrict__ out,
                                                                     const bf16* __restrict__ sink, float scale, int window, int H_all,
                                                                     const int* __restrict__ pos, const int* __restrict__ slot,
-                                                                    const int* __restrict__ block_table, int max_pages) {
+                                                                    const int* __restrict__ block_table, int max_pages, const HeadGate hg) {
   extern __shared__ uint4 smq[];
   pdl_wait();
   pdl_trigger();
@@ -399,12 +422,12 @@ __global__ void __launch_bounds__(256) latent_attention_mma_kernel(const LatentC
     const int d = (warp + 8 * i) * 8 + 2 * tq;
     if (d < R) {
       if (gq < H) {
-        const float inv = 1.0f / s_l[gq];
+        const float inv = head_gate(hg, r, h0 + gq) / s_l[gq];
         float* dst = out + ((size_t)r * H_all + h0 + gq) * R + d;
         dst[0] = o[i][0] * inv, dst[1] = o[i][1] * inv;
       }
       if (gq + 8 < H) {
-        const float inv = 1.0f / s_l[gq + 8];
+        const float inv = head_gate(hg, r, h0 + gq + 8) / s_l[gq + 8];
         float* dst = out + ((size_t)r * H_all + h0 + gq + 8) * R + d;
         dst[0] = o[i][2] * inv, dst[1] = o[i][3] * inv;
       }
@@ -414,7 +437,7 @@ __global__ void __launch_bounds__(256) latent_attention_mma_kernel(const LatentC
 
 template <int NBW>
 cudaError_t launch_attn_mma(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads, const int* pos,
-                            const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st) {
+                            const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st, const HeadGate& hg) {
   const int DP = c.rank + c.rot + 8;
   const size_t smem = (size_t)(16 + ATK) * DP * sizeof(bf16) + 16 * 65 * sizeof(float) + 16 * 72 * sizeof(bf16) + 48 * sizeof(float);
   if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
@@ -423,7 +446,7 @@ cudaError_t launch_attn_mma(const LatentCache& c, const float* qa, float* out, c
     if (r != cudaSuccess) return r;
   }
   return launch_k(latent_attention_mma_kernel<NBW>, dim3(n, (heads + 15) / 16), dim3(256), smem, st, c, qa, out, sink, scale, window, heads, pos, slot,
-                  block_table, max_pages);
+                  block_table, max_pages, hg);
 }
 
 size_t attn_smem_floats(int H, int D, int R, int TK) {
@@ -435,11 +458,11 @@ size_t attn_smem_floats(int H, int D, int R, int TK) {
 
 cudaError_t launch_latent_store(const LatentCache& c, const float* dkv, int ld, const bf16* w_norm, float eps, const RopeTable& rope,
                                 const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st,
-                                const QueryRope& qr) {
+                                const QueryRope& qr, const RowNorm& qn) {
   if (n <= 0) return cudaSuccess;
   if (c.elt_bytes == 4)
-    return launch_k(latent_store_kernel<float>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages, qr);
-  return launch_k(latent_store_kernel<bf16>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages, qr);
+    return launch_k(latent_store_kernel<float>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages, qr, qn);
+  return launch_k(latent_store_kernel<bf16>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages, qr, qn);
 }
 
 cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, float* dst, int ld_dst, int hs_dst, int heads, int rot,
@@ -450,7 +473,7 @@ cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, floa
 
 cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads,
                                     const int* pos, const int* slot, const int* block_table, int max_pages, int n, int max_keys, float* ws,
-                                    size_t ws_floats, cudaStream_t st) {
+                                    size_t ws_floats, cudaStream_t st, const HeadGate& hg) {
   if (n <= 0) return cudaSuccess;
   const int D = c.rank + c.rot;
   // bf16 cache rows and a prompt's worth of rows: tensor cores (QIE_ATTN_MMA=0 keeps the fp32 kernel)
@@ -458,10 +481,10 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
   if (mma_on && c.elt_bytes == 2 && n >= 64 && c.rank % 8 == 0 && c.rot % 8 == 0 && c.rank <= 512 && c.page_elems % 8 == 0 &&
       c.layer_off % 8 == 0 && (reinterpret_cast<uintptr_t>(c.pool) & 15) == 0) {
     cudaError_t r = cudaErrorInvalidConfiguration;
-    if (c.rank <= 64) r = launch_attn_mma<1>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
-    else if (c.rank <= 128) r = launch_attn_mma<2>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
-    else if (c.rank <= 256) r = launch_attn_mma<4>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
-    else r = launch_attn_mma<8>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
+    if (c.rank <= 64) r = launch_attn_mma<1>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st, hg);
+    else if (c.rank <= 128) r = launch_attn_mma<2>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st, hg);
+    else if (c.rank <= 256) r = launch_attn_mma<4>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st, hg);
+    else r = launch_attn_mma<8>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st, hg);
     if (r != cudaErrorInvalidConfiguration) return r;  // too large for its shared memory: the fp32 kernel below
   }
   // all heads of a row share the key tiles, so one CTA per row reads them once; with few rows the heads are dealt to
@@ -500,15 +523,15 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
     if (smem > 48 * 1024 && (r = cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
       return r;
     r = launch_k(latent_attention_kernel<float>, grid, dim3(256), smem, st, c, qa, out, sink, scale, window, heads, HG, TK, pos, slot, block_table,
-                    max_pages, n_splits, ws);
-    if (r == cudaSuccess && n_splits > 1) r = launch_k(latent_attention_combine_kernel, dim3(n, heads), dim3(128), 0, st, (const float*)ws, out, heads, c.rank, n_splits);
+                    max_pages, n_splits, ws, hg);
+    if (r == cudaSuccess && n_splits > 1) r = launch_k(latent_attention_combine_kernel, dim3(n, heads), dim3(128), 0, st, (const float*)ws, out, heads, c.rank, n_splits, hg);
     return r;
   }
   if (smem > 48 * 1024 && (r = cudaFuncSetAttribute(latent_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
     return r;
   r = launch_k(latent_attention_kernel<bf16>, grid, dim3(256), smem, st, c, qa, out, sink, scale, window, heads, HG, TK, pos, slot, block_table,
-               max_pages, n_splits, ws);
-  if (r == cudaSuccess && n_splits > 1) r = launch_k(latent_attention_combine_kernel, dim3(n, heads), dim3(128), 0, st, (const float*)ws, out, heads, c.rank, n_splits);
+               max_pages, n_splits, ws, hg);
+  if (r == cudaSuccess && n_splits > 1) r = launch_k(latent_attention_combine_kernel, dim3(n, heads), dim3(128), 0, st, (const float*)ws, out, heads, c.rank, n_splits, hg);
   return r;
 }
 

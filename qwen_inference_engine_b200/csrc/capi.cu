@@ -398,7 +398,7 @@ static void engine_free(qie_engine* e) {
   if (e->fam) {
     e->fam->release();
     delete e->fam;
-    e->fam = nullptr, e->ng = nullptr, e->fv = nullptr, e->dx = nullptr;
+    e->fam = nullptr, e->ng = nullptr, e->fv = nullptr, e->dx = nullptr, e->dd = nullptr;
   }
   if (!e->blob_owned) e->blob = nullptr;
   void* dev[] = {e->blob, e->cos_d, e->sin_d, e->kv.pool, e->block_table_d, e->ids_d, e->pos_d, e->slot_d,
@@ -1494,13 +1494,14 @@ const char* qie_model_families(void) { return registry_names(); }
 const char* qie_engine_family(const qie_engine* e) { return !e ? "" : (e->fam ? e->fam->family_name() : "qwen"); }
 
 static int create_family(qie_engine* e, int family, const std::string& arg, bool synthetic, uint64_t seed) {
-  if (family != FAMILY_NOGATAR && family != FAMILY_FOSAVIK && family != FAMILY_DITENEX) return fail(QIE_EINVAL, "family not handled here");
+  if (family != FAMILY_NOGATAR && family != FAMILY_FOSAVIK && family != FAMILY_DITENEX && family != FAMILY_DEDUNEX) return fail(QIE_EINVAL, "family not handled here");
   if (e->opts.tp_size > 1) return fail(QIE_EINVAL, "this family is not sharded (tp_size must be 1)");
   int code = QIE_EIO;
   std::string err;
   if (family == FAMILY_NOGATAR) err = synthetic ? nogatar_create_synthetic(e, arg, seed, &code) : nogatar_create(e, arg, &code);
   else if (family == FAMILY_FOSAVIK) err = synthetic ? fosavik_create_synthetic(e, arg, seed, &code) : fosavik_create(e, arg, &code);
-  else err = synthetic ? ditenex_create_synthetic(e, arg, seed, &code) : ditenex_create(e, arg, &code);
+  else if (family == FAMILY_DITENEX) err = synthetic ? ditenex_create_synthetic(e, arg, seed, &code) : ditenex_create(e, arg, &code);
+  else err = synthetic ? dedunex_create_synthetic(e, arg, seed, &code) : dedunex_create(e, arg, &code);
   if (!err.empty()) return fail(code, "%s", err.c_str());
   return QIE_OK;
 }

@@ -13,6 +13,7 @@
 
 #include "checkpoint.h"
 #include "kernels.h"
+#include "dedunex.h"
 #include "ditenex.h"
 #include "fosavik.h"
 #include "nogatar.h"
@@ -44,12 +45,13 @@ struct CaptureBuf {
 }  // namespace qie
 
 struct qie_engine {
-  // model family: Qwen (the members below named after its operators) unless `fam` is set (nogatar.h, fosavik.h, ditenex.h); sequences, pages,
+  // model family: Qwen (the members below named after its operators) unless `fam` is set (nogatar.h, fosavik.h, ditenex.h, dedunex.h); sequences, pages,
   // block tables, row metadata, sampling and graphs are shared by the families
-  qie::RowFamily* fam = nullptr;  // the family's interface (family.h); ng / fv / dx below are the same object, typed
+  qie::RowFamily* fam = nullptr;  // the family's interface (family.h); ng / fv / dx / dd below are the same object, typed
   qie::NgModel* ng = nullptr;
   qie::FvModel* fv = nullptr;
   qie::DxModel* dx = nullptr;
+  qie::DdModel* dd = nullptr;
   qie_config cfg{};
   qie_engine_opts opts{};
   int num_sms = 0;

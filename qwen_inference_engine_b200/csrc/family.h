@@ -51,7 +51,7 @@ struct TensorSpec {
   std::string name;
   size_t rows = 0, cols = 0;  // cols 0 = vector of `rows`
   size_t off = 0;             // element offset in the blob
-  int kind = 0;               // synthetic fill: 0 matrix (uniform, variance 1/cols), 1 norm weight (about 1), 2 small vector
+  int kind = 0;               // synthetic fill: 0 matrix (uniform, variance 1/cols), 1 norm weight (about 1), 2 small vector; 3: zeros that no file holds
   size_t elems() const { return rows * (cols ? cols : 1); }
 };
 // appends tensors to a layout; pad() starts the next group on a 256-byte boundary (tensors that one GEMM reads as a
@@ -73,6 +73,31 @@ uint16_t f32_to_bf16_bits(float f);
 void fill_synthetic_blob(const std::vector<TensorSpec>& t, uint64_t seed, std::vector<uint16_t>* blob);
 // reads every tensor of the layout from a safetensors file (BF16 only; shapes are checked by element count) -> "" or the error
 std::string load_safetensors_blob(const std::string& path, const std::vector<TensorSpec>& t, std::vector<uint16_t>* blob);
+
+// ---------------------------------------------------------------- rotary positions
+// Rotation angles of position p: a_i = p * f_i, f_i = base^(-2i / dims), i < dims / 2.  With `scaled` (YaRN) the
+// frequencies are blended: with corr(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(corr(fast)), 0),
+// hi = min(ceil(corr(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
+// f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1.
+struct RotaryCfg {
+  int dims = 0;
+  double base = 10000.0;
+  bool scaled = false;
+  double factor = 1.0, original = 0.0, fast = 0.0, slow = 0.0;
+  bool operator==(const RotaryCfg& o) const {
+    return dims == o.dims && base == o.base && scaled == o.scaled && factor == o.factor && original == o.original && fast == o.fast &&
+           slow == o.slow;
+  }
+};
+// cos / sin tables [context, dims / 2], worked out in double, the magnitude factor folded in
+void rotary_tables(const RotaryCfg& r, int context, std::vector<float>* c, std::vector<float>* s);
+// what the kernels read: the tables on the device and how the rotated dimensions pair up
+struct RopeTable {
+  const float* cos_t = nullptr;  // [context, dims/2], scaled by the magnitude factor
+  const float* sin_t = nullptr;
+  int dims = 0;         // rotated leading dimensions
+  int half_layout = 0;  // 0: pairs (2i, 2i+1); 1: pairs (i, i + dims/2)
+};
 
 // ---------------------------------------------------------------- projections on the tcgen05 GEMM
 // C[n, N] = A[n, K] W[N, K]^T in bf16 serving precision and for more than 16 rows: A rows -> dense bf16, the tcgen05

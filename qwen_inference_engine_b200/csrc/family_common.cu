@@ -1,6 +1,7 @@
 // family_common.cu -- see family.h: weight blob helpers and the tcgen05 projection helper of the row-forward families.
 #include "family.h"
 
+#include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -44,6 +45,7 @@ static float hash_uniform(uint64_t seed, uint64_t i) {
 void fill_synthetic_blob(const std::vector<TensorSpec>& t, uint64_t seed, std::vector<uint16_t>* blob) {
   for (size_t k = 0; k < t.size(); ++k) {
     const TensorSpec& s = t[k];
+    if (s.kind == 3) continue;  // zero rows between the parts of a fused matrix
     const float a = s.kind == 0 ? sqrtf(3.0f / (float)s.cols) : 0.f;
     for (size_t i = 0; i < s.elems(); ++i) {
       const float u = hash_uniform(seed + 1315423911ull * k, i);
@@ -68,6 +70,7 @@ std::string load_safetensors_blob(const std::string& path, const std::vector<Ten
   if (!JsonReader::parse(hdr.data(), hdr.data() + hdr.size(), &root, &err)) return fclose(f), path + ": " + err;
   const size_t data0 = 8 + (size_t)hl;
   for (const TensorSpec& s : t) {
+    if (s.kind == 3) continue;  // not in the file: zero rows between the parts of a fused matrix
     const JsonValue* rec = root.have(s.name.c_str());
     if (!rec) return fclose(f), "tensor " + s.name + " missing in " + path;
     const JsonValue* dt = rec->have("dtype");
@@ -115,6 +118,30 @@ cudaError_t RowFamily::sample_rows(qie_engine* e, int n_out, float temperature, 
   }
   if (advance) FAM_TRY(KK_ADVANCE, launch_advance(e->pos_d, e->ids_d, e->sampled_d, n_out, e->rowstep_d, st));
   return cudaSuccess;
+}
+
+void rotary_tables(const RotaryCfg& r, int context, std::vector<float>* c, std::vector<float>* s) {
+  const int half = r.dims / 2;
+  std::vector<double> f(half);
+  double mag = 1.0;
+  for (int i = 0; i < half; ++i) f[i] = pow(r.base, -2.0 * i / r.dims);
+  if (r.scaled) {
+    const double PI = 3.14159265358979323846;
+    auto corr = [&](double turns) { return r.dims * log(r.original / (2.0 * PI * turns)) / (2.0 * log(r.base)); };
+    const double lo = std::max(floor(corr(r.fast)), 0.0), hi = std::min(ceil(corr(r.slow)), (double)(r.dims - 1));
+    for (int i = 0; i < half; ++i) {
+      const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
+      f[i] = f[i] / r.factor * ramp + f[i] * (1.0 - ramp);
+    }
+    mag = 0.1 * log(r.factor) + 1.0;
+  }
+  c->resize((size_t)context * half);
+  s->resize((size_t)context * half);
+  for (int p = 0; p < context; ++p)
+    for (int i = 0; i < half; ++i) {
+      (*c)[(size_t)p * half + i] = (float)(cos(p * f[i]) * mag);
+      (*s)[(size_t)p * half + i] = (float)(sin(p * f[i]) * mag);
+    }
 }
 
 cudaError_t TcProjector::alloc(size_t rows, size_t max_k, size_t max_n, cudaStream_t st) {

@@ -65,6 +65,9 @@ struct KvRowCache {
 // Optional: biases added to keys and values first; values blended with another layer's values of the same rows,
 // v = (1 - lam) v + lam v_other (lam one bf16 number on the device); the stored values also kept as fp32 rows (v_keep);
 // the head-mixed queries of the row (TalkQueries below) written in the same launch.
+// Rotary positions (rope.dims > 0): after the norm, the first rope.dims elements of every `norm_dim` consecutive elements
+// of the keys and of the queries are rotated by the row's position (with two score maps every map of every head is such a
+// group); q_bias is added to the queries before their norm.
 // Mixing the heads' scores before the softmax, score'_h = sum_g talk[h, g] score_g, is linear in the queries: with
 // qt[r, h, c * dim + e] = sum over the heads g of kv head c of talk[h, g] * (q[r, g, e] + q_bias[g * dim + e])
 // head h's mixed score against key j is qt[r, h, :] . [keys of all kv heads of j] (GqaAttnArgs::shared_keys), and distance
@@ -91,6 +94,8 @@ struct KvStoreArgs {
   const bf16* q_norm = nullptr;
   const bf16* k_bias = nullptr;  // [kw]
   const bf16* v_bias = nullptr;  // [vw]
+  const bf16* q_bias = nullptr;  // [q_heads * norm_dim]
+  RopeTable rope;
   const bf16* v_lam = nullptr;
   const float* v_other = nullptr;
   int ld_vo = 0;
@@ -106,6 +111,7 @@ cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st);
 // head h / (heads / kv_heads).  unit_sink adds 1 to every softmax denominator (as if one more key with a zero score and nothing to contribute took part).
 // finish 0: out = a_1;  1: out = a_1 * sigmoid(gate[r, h]);  2 (maps == 2): o = a_1 - lam * a_2, out = o / sqrt(mean(o^2) + eps) * post;
 // 3: out[r, h, c] = a_1[c] * sigmoid(gate[r, h * vdim + c]) (a gate per element).
+// softcap > 0: the scaled score s becomes softcap * tanh(s / softcap) before the mask, the slopes and the softmax.
 // slopes (optional, [heads] fp32): slopes[h] * (pos - j) is taken off the scaled score of key j (a linear distance penalty).
 // shared_keys: every head scores against the WHOLE key part of the cached row (dim = kw / maps elements: the keys of all
 // kv heads side by side) while its values stay those of kv head h / (heads / kv_heads); the queries are then
@@ -120,7 +126,7 @@ struct GqaAttnArgs {
   bf16* out_bf = nullptr;  // maps == 1: the result goes here as bf16 rows (row stride ldo_bf) instead of `out`
   int ldo_bf = 0;
   int heads = 0, kv_heads = 0, dim = 0, vdim = 0, maps = 1;
-  float scale = 1.f;
+  float scale = 1.f, softcap = 0.f;
   int window = 0, keep_first = 0, unit_sink = 0;
   int finish = 0;
   const float* gate = nullptr;

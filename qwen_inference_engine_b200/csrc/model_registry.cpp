@@ -23,6 +23,7 @@ const Row kRegistry[] = {
     {"Nogatar", FAMILY_NOGATAR},
     {"Fosavik", FAMILY_FOSAVIK},
     {"Ditenex", FAMILY_DITENEX},
+    {"Dedunex", FAMILY_DEDUNEX},
     {"Qwen2ForCausalLM", FAMILY_QWEN},
     {"Qwen3ForCausalLM", FAMILY_QWEN},
 };

@@ -6,7 +6,7 @@
 
 namespace qie {
 
-enum ModelFamily { FAMILY_QWEN = 0, FAMILY_NOGATAR = 1, FAMILY_FOSAVIK = 2, FAMILY_DITENEX = 3 };
+enum ModelFamily { FAMILY_QWEN = 0, FAMILY_NOGATAR = 1, FAMILY_FOSAVIK = 2, FAMILY_DITENEX = 3, FAMILY_DEDUNEX = 4 };
 
 // comma-separated architecture names the registry knows
 const char* registry_names();

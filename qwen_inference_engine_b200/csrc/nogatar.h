@@ -82,11 +82,6 @@ struct LatentCache {
   size_t layer_off = 0;
   int rank = 0, rot = 0;  // width = rank + rot
 };
-struct RopeTable {
-  const float* cos_t = nullptr;  // [context, dims/2], scaled by the magnitude factor
-  const float* sin_t = nullptr;
-  int dims = 0;  // rotated leading dimensions (pairs (2i, 2i+1))
-};
 // optional rider of launch_latent_store: rotary positions on src[r, h, 0:rot] -> dst[r, h, 0:rot] of the row's query heads
 struct QueryRope {
   const float* src = nullptr;
@@ -94,10 +89,21 @@ struct QueryRope {
   float* dst = nullptr;
   int ld_dst = 0, hs_dst = 0, heads = 0;
 };
+// optional rider of launch_latent_store: dst[r, 0:width] = src[r, 0:width] / sqrt(mean(src^2) + eps) * w (fp32 rows and / or
+// dense bf16 rows), the norm of a low-rank query latent that sits in the same projection output as the key/value latent
+struct RowNorm {
+  const float* src = nullptr;
+  int ld_src = 0, width = 0;
+  const bf16* w = nullptr;
+  float* dst = nullptr;
+  int ld_dst = 0;
+  bf16* dst_bf = nullptr;
+  int ld_dst_bf = 0;
+};
 // per row: latent = rms_unit(dkv[:rank]) * w_norm, key = rope(dkv[rank:], pos) -> cache row (slot, pos)
 cudaError_t launch_latent_store(const LatentCache& c, const float* dkv, int ld, const bf16* w_norm, float eps, const RopeTable& rope,
                                 const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st,
-                                const QueryRope& qr = QueryRope());
+                                const QueryRope& qr = QueryRope(), const RowNorm& qn = RowNorm());
 // rotary positions on src[r, h, 0:rot] -> dst[r, h, 0:rot] (row strides ld_*, head strides hs_*)
 cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, float* dst, int ld_dst, int hs_dst, int heads, int rot,
                                   const RopeTable& rope, const int* pos, int n, cudaStream_t st);
@@ -106,9 +112,16 @@ cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, floa
 // with `sink` the denominator also holds exp(sink[h]).  qa rows are heads * (rank + rot), out rows heads * rank.
 // max_keys bounds pos + 1 over the rows; with a workspace (ws, ws_floats) and few rows the keys of a row are split
 // over several CTAs and combined (needs rows * heads * splits * (rank + 2) floats).
+// With a head gate the result of (row, head) is multiplied by sigmoid(z[r, h] + bias[h]) (one number per head commutes with
+// the value up-projection that follows, so it is applied to the attended latent).
+struct HeadGate {
+  const float* z = nullptr;  // [n, ld] pre-activations, head h at column h; null: no gate
+  int ld = 0;
+  const bf16* bias = nullptr;
+};
 cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads,
                                     const int* pos, const int* slot, const int* block_table, int max_pages, int n, int max_keys, float* ws,
-                                    size_t ws_floats, cudaStream_t st);
+                                    size_t ws_floats, cudaStream_t st, const HeadGate& hg = HeadGate());
 
 // ---------------------------------------------------------------- mLSTM (mlstm.cu)
 // Recurrent state of one (sequence slot, layer), fp32: S [heads][dim][vdim], then n [heads][blocks][dim] and
@@ -164,16 +177,7 @@ bool grouped_gemm_bf16_fits(const GroupedGemmBf16& g);  // K a multiple of 32, 1
 cudaError_t launch_grouped_gemm_bf16(const GroupedGemmBf16& g, cudaStream_t st);
 
 // ---------------------------------------------------------------- the model (nogatar_model.cu)
-struct NgRot {
-  int dims = 0;
-  double base = 10000.0;
-  bool scaled = false;
-  double factor = 1.0, original = 0.0, fast = 0.0, slow = 0.0;
-  bool operator==(const NgRot& o) const {
-    return dims == o.dims && base == o.base && scaled == o.scaled && factor == o.factor && original == o.original && fast == o.fast &&
-           slow == o.slow;
-  }
-};
+typedef RotaryCfg NgRot;
 struct NgLayer {
   int type = 0;  // 0 latent_attention, 1 mlstm
   // mixers

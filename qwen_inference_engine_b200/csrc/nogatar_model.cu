@@ -152,30 +152,6 @@ size_t layout_elems(const std::vector<TensorSpec>& t) { return t.empty() ? 0 : t
     }                                                                  \
   } while (0)
 
-void rope_tables(const NgRot& r, int context, std::vector<float>* c, std::vector<float>* s) {
-  const int half = r.dims / 2;
-  std::vector<double> f(half);
-  double mag = 1.0;
-  for (int i = 0; i < half; ++i) f[i] = pow(r.base, -2.0 * i / r.dims);
-  if (r.scaled) {
-    const double PI = 3.14159265358979323846;
-    auto corr = [&](double turns) { return r.dims * log(r.original / (2.0 * PI * turns)) / (2.0 * log(r.base)); };
-    const double lo = std::max(floor(corr(r.fast)), 0.0), hi = std::min(ceil(corr(r.slow)), (double)(r.dims - 1));
-    for (int i = 0; i < half; ++i) {
-      const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
-      f[i] = f[i] / r.factor * ramp + f[i] * (1.0 - ramp);
-    }
-    mag = 0.1 * log(r.factor) + 1.0;
-  }
-  c->resize((size_t)context * half);
-  s->resize((size_t)context * half);
-  for (int p = 0; p < context; ++p)
-    for (int i = 0; i < half; ++i) {
-      (*c)[(size_t)p * half + i] = (float)(cos(p * f[i]) * mag);
-      (*s)[(size_t)p * half + i] = (float)(sin(p * f[i]) * mag);
-    }
-}
-
 std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const std::vector<uint16_t>& blob, int* code) {
   NgModel* m = e->ng;
   const qie_engine_opts& o = e->opts;
@@ -250,7 +226,7 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   // rotary tables
   for (const NgRot& r : m->rope_cfg) {
     std::vector<float> c, s;
-    rope_tables(r, o.context, &c, &s);
+    rotary_tables(r, o.context, &c, &s);
     float *cd = nullptr, *sd = nullptr;
     if (!c.empty()) {
       CUS(cudaMalloc(&cd, c.size() * sizeof(float)));

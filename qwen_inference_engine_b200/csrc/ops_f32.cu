@@ -3,6 +3,7 @@
 // grouped, gathered) and the logit soft cap.  Every reduction has a fixed order per row, so a row's result does
 // not depend on the rows it shares a launch with.
 #include "launch.h"
+#include "dedunex.h"
 #include "nogatar.h"
 
 namespace qie {
@@ -476,12 +477,12 @@ __global__ void rows_f32_to_bf16_kernel(const float* __restrict__ in, int ld_in,
 }
 
 // dense bf16 rows -> rows of a strided fp32 matrix, with the activation of GemmF32::act
-__global__ void rows_bf16_to_f32_kernel(const bf16* __restrict__ in, int cols, float* __restrict__ out, int ld_out, int act) {
+__global__ void rows_bf16_to_f32_kernel(const bf16* __restrict__ in, int ld_in, int cols, float* __restrict__ out, int ld_out, int act) {
   pdl_wait();
   pdl_trigger();
-  const bf16* src = in + (size_t)blockIdx.x * cols;
+  const bf16* src = in + (size_t)blockIdx.x * ld_in;
   float* dst = out + (size_t)blockIdx.x * ld_out;
-  if (act == 0 && cols % 8 == 0 && ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+  if (act == 0 && cols % 8 == 0 && ld_in % 8 == 0 && ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
     for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 8) {  // 8 elements per 16-byte load
       const uint4 p = *reinterpret_cast<const uint4*>(src + i);
       *reinterpret_cast<float4*>(dst + i) = make_float4(lo2f(p.x), hi2f(p.x), lo2f(p.y), hi2f(p.y));
@@ -553,7 +554,12 @@ cudaError_t launch_rows_f32_to_bf16(const float* in, int ld_in, const int* row_i
 
 cudaError_t launch_rows_bf16_to_f32(const bf16* in, int cols, float* out, int ld_out, int act, int n, cudaStream_t st) {
   if (n <= 0) return cudaSuccess;
-  return launch_k(rows_bf16_to_f32_kernel, dim3(n), dim3(256), 0, st, in, cols, out, ld_out, act);
+  return launch_k(rows_bf16_to_f32_kernel, dim3(n), dim3(256), 0, st, in, cols, cols, out, ld_out, act);
+}
+
+cudaError_t launch_rows_bf16_to_f32_ld(const bf16* in, int ld_in, int cols, float* out, int ld_out, int n, cudaStream_t st) {
+  if (n <= 0 || cols <= 0) return cudaSuccess;
+  return launch_k(rows_bf16_to_f32_kernel, dim3(n), dim3(256), 0, st, in, ld_in, cols, out, ld_out, 0);
 }
 
 cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, cudaStream_t st) {

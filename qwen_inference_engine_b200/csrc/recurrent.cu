@@ -1,10 +1,11 @@
 // recurrent.cu -- the short causal convolution and the two linear recurrences of the fp32-stream families
 // (fosavik.h): the real-gated linear recurrent unit of Griffin (one state per channel) and the state-space recurrence
 // of Mamba-2 (a state matrix per head), with the gated group norm behind it and the clamped gated activation of the
-// feed-forward.  A launch walks SEGMENTS: runs of consecutive rows of one sequence, whose state lives in the
+// feed-forward; and the minGRU recurrence (dedunex.h: one state per channel, gates that read only the current token).  A launch walks SEGMENTS: runs of consecutive rows of one sequence, whose state lives in the
 // sequence's slot and is carried from call to call.  Everything that enters a recurrence is fp32.
 #include <algorithm>
 
+#include "dedunex.h"
 #include "fosavik.h"
 #include "launch.h"
 
@@ -193,6 +194,137 @@ __global__ void __launch_bounds__(128) lru_chunk_apply_kernel(const LruArgs a) {
   for (int t = t0; t < t1; ++t) {
     const float S = fmaf(a.zr[(size_t)t * a.ldz + c], Sin, a.out[(size_t)t * a.ldo + c]);
     a.out[(size_t)t * a.ldo + c] = S * gelu_tanhf_(a.yb[(size_t)t * a.ldy + c] + yb);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// minGRU: S = (1 - z) S + z cand, one state per channel.  The gate z = sigmoid(zp), so the decay 1 - z is sigmoid(-zp)
+// (exact where z is close to 1); the candidate is u + 1/2 for u >= 0 and sigmoid(u) below (continuous at 0).
+__device__ __forceinline__ float mg_ld(const float* f, const bf16* b, size_t i) { return f ? f[i] : bf2f(b[i]); }
+__device__ __forceinline__ void mg_gates(float zp, float u, float* decay, float* in) {
+  const float z = sigmoidf_(zp);
+  *decay = sigmoidf_(-zp);
+  *in = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
+}
+__device__ __forceinline__ void mg_store(const MinGruArgs& a, size_t t, int c, float S, float gp) {
+  const float v = S * siluf_(gp);
+  if (a.out) a.out[t * a.ldo + c] = v;
+  if (a.out_bf) a.out_bf[t * a.ldo_bf + c] = f2bf(v);
+}
+constexpr int MG_PF = 16;  // rows whose loads a scan thread keeps in flight
+
+// thread (segment, channel) walks the segment's rows
+__global__ void __launch_bounds__(64) mingru_scan_kernel(const MinGruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const size_t ld = a.zp ? a.ld : a.ld_bf;
+  float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + c;
+  float S = *sp;
+  const float zb = a.z_bias ? bf2f(a.z_bias[c]) : 0.f, ub = a.u_bias ? bf2f(a.u_bias[c]) : 0.f;
+  for (int t0 = r0; t0 < r1; t0 += MG_PF) {
+    float zv[MG_PF], uv[MG_PF], gv[MG_PF];
+#pragma unroll
+    for (int k = 0; k < MG_PF; ++k) {
+      const size_t t = min(t0 + k, r1 - 1);
+      zv[k] = mg_ld(a.zp, a.zp_bf, t * ld + c);
+      uv[k] = mg_ld(a.up, a.up_bf, t * ld + c);
+      gv[k] = mg_ld(a.gp, a.gp_bf, t * ld + c);
+    }
+#pragma unroll
+    for (int k = 0; k < MG_PF; ++k) {
+      if (t0 + k < r1) {
+        float d, in;
+        mg_gates(zv[k] + zb, uv[k] + ub, &d, &in);
+        S = fmaf(d, S, in);
+        mg_store(a, (size_t)(t0 + k), c, S, gv[k]);
+      }
+    }
+  }
+  *sp = S;
+}
+
+// The same recurrence for long portions in three parallel steps over chunks of MG_CHUNK rows (a chunk starts a multiple
+// of MG_CHUNK rows from its segment's start).  (1) every chunk runs from a zero state: the local states and the running
+// product of the decays go to the workspace, the chunk's total decay P and end state Q to its summary; (2) one thread per
+// channel carries the true state over the chunks; (3) S_t = local_t + decay_t * S_in, times the output gate.
+// Workspace: local [n_rows, channels] | cum [n_rows, channels] | summaries [ids, 2, channels].
+constexpr int MG_CHUNK = 64;
+__device__ __forceinline__ int mg_chunk_id(int r0, int seg, int k) { return r0 / MG_CHUNK + seg + k; }  // unique over the batch
+
+__global__ void __launch_bounds__(64) mingru_chunk_local_kernel(const MinGruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x, k = blockIdx.z;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const int t0 = r0 + k * MG_CHUNK, t1 = min(r1, t0 + MG_CHUNK);
+  if (t0 >= r1 || c >= a.channels) return;
+  const size_t ld = a.zp ? a.ld : a.ld_bf, C = a.channels;
+  float* local = a.ws;
+  float* cumw = a.ws + (size_t)a.n_rows * C;
+  float* sums = cumw + (size_t)a.n_rows * C;
+  const float zb = a.z_bias ? bf2f(a.z_bias[c]) : 0.f, ub = a.u_bias ? bf2f(a.u_bias[c]) : 0.f;
+  float S = 0.f, cum = 1.f;
+  for (int tb = t0; tb < t1; tb += MG_PF) {
+    float zv[MG_PF], uv[MG_PF];
+#pragma unroll
+    for (int j = 0; j < MG_PF; ++j) {
+      const size_t t = min(tb + j, t1 - 1);
+      zv[j] = mg_ld(a.zp, a.zp_bf, t * ld + c);
+      uv[j] = mg_ld(a.up, a.up_bf, t * ld + c);
+    }
+#pragma unroll
+    for (int j = 0; j < MG_PF; ++j) {
+      if (tb + j < t1) {
+        float d, in;
+        mg_gates(zv[j] + zb, uv[j] + ub, &d, &in);
+        S = fmaf(d, S, in);
+        cum *= d;
+        local[(size_t)(tb + j) * C + c] = S;
+        cumw[(size_t)(tb + j) * C + c] = cum;
+      }
+    }
+  }
+  float* w = sums + (size_t)mg_chunk_id(r0, seg, k) * 2 * C;
+  w[c] = cum;
+  w[C + c] = S;
+}
+
+__global__ void __launch_bounds__(64) mingru_chunk_carry_kernel(const MinGruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const size_t C = a.channels;
+  float* sums = a.ws + 2 * (size_t)a.n_rows * C;
+  float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + c;
+  float S = *sp;
+  for (int k = 0; r0 + k * MG_CHUNK < r1; ++k) {
+    float* w = sums + (size_t)mg_chunk_id(r0, seg, k) * 2 * C;
+    const float P = w[c], Q = w[C + c];
+    w[c] = S;  // the chunk's incoming state
+    S = fmaf(P, S, Q);
+  }
+  *sp = S;
+}
+
+__global__ void __launch_bounds__(128) mingru_chunk_apply_kernel(const MinGruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x, k = blockIdx.z;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const int t0 = r0 + k * MG_CHUNK, t1 = min(r1, t0 + MG_CHUNK);
+  if (t0 >= r1 || c >= a.channels) return;
+  const size_t ld = a.zp ? a.ld : a.ld_bf, C = a.channels;
+  const float* local = a.ws;
+  const float* cumw = a.ws + (size_t)a.n_rows * C;
+  const float Sin = cumw[(size_t)a.n_rows * C + (size_t)mg_chunk_id(r0, seg, k) * 2 * C + c];
+  for (int t = t0; t < t1; ++t) {
+    const float S = fmaf(cumw[(size_t)t * C + c], Sin, local[(size_t)t * C + c]);
+    mg_store(a, (size_t)t, c, S, mg_ld(a.gp, a.gp_bf, (size_t)t * ld + c));
   }
 }
 
@@ -387,6 +519,20 @@ cudaError_t launch_lru_scan(const LruArgs& a, cudaStream_t st) {
     return launch_k(lru_chunk_apply_kernel, dim3(a.n_seg, (a.channels + 127) / 128, chunks), dim3(128), 0, st, a);
   }
   return launch_k(lru_scan_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a);
+}
+
+cudaError_t launch_mingru_scan(const MinGruArgs& a, cudaStream_t st) {
+  if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
+  if (!(a.zp && a.up && a.gp) && !(a.zp_bf && a.up_bf && a.gp_bf)) return cudaErrorInvalidValue;
+  if ((!a.out && !a.out_bf) || !a.state || a.channels <= 0) return cudaErrorInvalidValue;
+  if (a.ws && a.n_rows >= 4 * MG_CHUNK && a.n_seg <= 64 && mingru_ws_floats(a.n_rows, a.n_seg, a.channels) <= a.ws_floats) {
+    const int chunks = (a.n_rows + MG_CHUNK - 1) / MG_CHUNK;
+    cudaError_t r = launch_k(mingru_chunk_local_kernel, dim3(a.n_seg, (a.channels + 63) / 64, chunks), dim3(64), 0, st, a);
+    if (r != cudaSuccess) return r;
+    if ((r = launch_k(mingru_chunk_carry_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a)) != cudaSuccess) return r;
+    return launch_k(mingru_chunk_apply_kernel, dim3(a.n_seg, (a.channels + 127) / 128, chunks), dim3(128), 0, st, a);
+  }
+  return launch_k(mingru_scan_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a);
 }
 
 cudaError_t launch_ssd_scan(const SsdArgs& a, cudaStream_t st) {

@@ -1,7 +1,10 @@
 // rmsnorm_f32.cu -- RMS norms of a model whose sublayers sit between two norms (ditenex.h): the output norm folded
 // into the residual add together with the next sublayer's input norm, and the input norm of a mixer that reads a blend
-// of each row with the row before it (token shift) with one carried row per sequence slot.  All fp32, one CTA per row,
-// every reduction in a fixed order per row, so a row's result does not depend on the rows it shares a launch with.
+// of each row with the row before it (token shift) with one carried row per sequence slot; and the grouped RMS norm of a
+// model of parallel blocks (dedunex.h): the residual add of the two sublayer outputs and the next block's norm in one kernel.
+// All fp32, one CTA per row, every reduction in a fixed order per row, so a row's result does not depend on the rows it
+// shares a launch with.
+#include "dedunex.h"
 #include "ditenex.h"
 #include "launch.h"
 #include "moe_route.cuh"
@@ -210,7 +213,132 @@ __global__ void __launch_bounds__(256) rms_shift_kernel(const RmsShiftArgs a) {
   }
 }
 
+
+// The row lies in shared memory.  Each of the `groups` parts is normed by a team of warps: with fewer groups than warps a
+// group gets blockDim / 32 / groups warps whose partial sums meet in shared memory in a fixed order, else a warp walks the
+// groups warp, warp + nw, ...  scale[g] receives 1 / sqrt(mean + eps) of every group.
+__device__ __forceinline__ void group_rstd(const float* row, int W, int groups, float eps, float* red, float* scale) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, gs = W / groups;
+  if (groups >= nw) {
+    for (int g = warp; g < groups; g += nw) {
+      float s = 0.f;
+      for (int i = lane; i < gs; i += 32) s = fmaf(row[g * gs + i], row[g * gs + i], s);
+      s = warp_sum(s);
+      if (lane == 0) scale[g] = 1.0f / sqrtf(s / (float)gs + eps);
+    }
+  } else {
+    const int wpg = nw / groups, g = warp / wpg, k = warp % wpg;
+    float s = 0.f;
+    if (g < groups)
+      for (int i = k * 32 + lane; i < gs; i += 32 * wpg) s = fmaf(row[g * gs + i], row[g * gs + i], s);
+    s = warp_sum(s);
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (threadIdx.x < groups) {
+      float t = 0.f;
+      for (int j = 0; j < wpg; ++j) t += red[threadIdx.x * wpg + j];
+      scale[threadIdx.x] = 1.0f / sqrtf(t / (float)gs + eps);
+    }
+  }
+  __syncthreads();
+}
+
+template <int V>
+__global__ void __launch_bounds__(256) group_norm_step_kernel(const GroupNormStep a) {
+  extern __shared__ __align__(16) float row[];  // [width], then [groups] scales
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, W = a.width, gs = W / a.groups;
+  float* scale = row + W;
+  const int t0 = threadIdx.x * V, step = blockDim.x * V;
+  const int src = a.gather ? a.gather[r] : r;
+  float* xr = a.x + (size_t)src * W;
+  bool changed = false;
+  if (a.ids) {  // the embedding row, normed
+    const bf16* er = a.embed + (size_t)a.ids[r] * W;
+    for (int i = t0; i < W; i += step) st_f32<V>(row + i, ld_bf16<V>(er + i));
+    __syncthreads();
+    group_rstd(row, W, a.groups, a.eps, red, scale);
+    for (int i = t0; i < W; i += step) {
+      Pack<V> v = ld_f32<V>(row + i);
+      const Pack<V> w = ld_bf16<V>(a.w_pre + i);
+#pragma unroll
+      for (int u = 0; u < V; ++u) v.v[u] = v.v[u] * scale[(i + u) / gs] * w.v[u];
+      st_f32<V>(row + i, v);
+    }
+    changed = true;
+  } else {
+    for (int i = t0; i < W; i += step) st_f32<V>(row + i, ld_f32<V>(xr + i));
+  }
+  // every thread touches only its own elements of the row until the norm below
+  if (a.y1 || a.y1_bf || a.y2 || a.y2_bf) {
+    for (int i = t0; i < W; i += step) {
+      Pack<V> v = ld_f32<V>(row + i);
+      if (a.y1 || a.y1_bf) {
+        const Pack<V> y = a.y1_bf ? ld_bf16<V>(a.y1_bf + (size_t)src * W + i) : ld_f32<V>(a.y1 + (size_t)src * W + i);
+        if (a.y2 || a.y2_bf) {
+          const Pack<V> z = a.y2_bf ? ld_bf16<V>(a.y2_bf + (size_t)src * W + i) : ld_f32<V>(a.y2 + (size_t)src * W + i);
+#pragma unroll
+          for (int u = 0; u < V; ++u) v.v[u] += y.v[u] + z.v[u];
+        } else {
+#pragma unroll
+          for (int u = 0; u < V; ++u) v.v[u] += y.v[u];
+        }
+      } else {
+        const Pack<V> z = a.y2_bf ? ld_bf16<V>(a.y2_bf + (size_t)src * W + i) : ld_f32<V>(a.y2 + (size_t)src * W + i);
+#pragma unroll
+        for (int u = 0; u < V; ++u) v.v[u] += z.v[u];
+      }
+      st_f32<V>(row + i, v);
+    }
+    changed = true;
+  }
+  if (a.dump)
+    for (int i = t0; i < W; i += step) st_f32<V>(a.dump + (size_t)r * W + i, ld_f32<V>(row + i));
+  if (a.step) {
+    for (int i = t0; i < W; i += step) {
+      Pack<V> v = ld_f32<V>(row + i);
+      const Pack<V> s = ld_bf16<V>(a.step + i);
+#pragma unroll
+      for (int u = 0; u < V; ++u) v.v[u] += s.v[u];
+      st_f32<V>(row + i, v);
+    }
+    changed = true;
+  }
+  if (changed)
+    for (int i = t0; i < W; i += step) st_f32<V>(xr + i, ld_f32<V>(row + i));
+  if (!a.h && !a.h_bf) return;
+  __syncthreads();
+  group_rstd(row, W, a.groups, a.eps, red, scale);
+  for (int i = t0; i < W; i += step) {
+    const Pack<V> x = ld_f32<V>(row + i), w = ld_bf16<V>(a.w_in + i);
+    Pack<V> o;
+#pragma unroll
+    for (int u = 0; u < V; ++u) o.v[u] = x.v[u] * scale[(i + u) / gs] * w.v[u];
+    if (a.h) st_f32<V>(a.h + (size_t)r * W + i, o);
+    if (a.h_bf) st_bf16<V>(a.h_bf + (size_t)r * W + i, o);
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_group_norm_step(const GroupNormStep& a, cudaStream_t st) {
+  if (a.n <= 0) return cudaSuccess;
+  const bool read = a.h || a.h_bf;
+  if (a.width <= 0 || a.groups <= 0 || a.width % a.groups || (read && !a.w_in) || (a.ids && (!a.embed || !a.w_pre || a.gather))) return cudaErrorInvalidValue;
+  const size_t smem = ((size_t)a.width + a.groups) * sizeof(float);
+  auto al = [](const void* p, size_t b) { return (reinterpret_cast<uintptr_t>(p) & (b - 1)) == 0; };
+  const bool vec = a.width % 4 == 0 && al(a.x, 16) && al(a.y1, 16) && al(a.y2, 16) && al(a.y1_bf, 8) && al(a.y2_bf, 8) && al(a.dump, 16) && al(a.h, 16) &&
+                   al(a.h_bf, 8) && al(a.w_in, 8) && al(a.w_pre, 8) && al(a.step, 8) && al(a.embed, 8);
+  auto* kern = vec ? group_norm_step_kernel<4> : group_norm_step_kernel<1>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    cudaError_t r = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(kern, dim3(a.n), dim3(256), smem, st, a);
+}
 
 cudaError_t launch_rms_step(const RmsStep& a, cudaStream_t st) {
   if (a.n <= 0) return cudaSuccess;
