@@ -485,6 +485,41 @@ def ditenex_macs_per_token(cfg):
     return mac
 
 
+def dedunex_config(z, vocab=32000):
+    """three layers, four layer runs: minGRU, differential window attention (run twice by the loop, with rotary positions,
+    soft-capped scores and two kv heads), latent attention behind a query bottleneck; gated feed-forwards of the compared
+    Qwen model's width behind the same norm as the mixers"""
+    W = z["width"]
+    ff = {"ff": z["top"] * z["ff"] + z["sff"], "kind": "dense"}
+    att = {"diff": 0.8, "dim": 64, "heads": W // 128, "kv_heads": 2, "mask": {"size": z["window"]}, "scale": 0.125, "softcap": 30.0, "vdim": 128,
+           "rot": {"base": 10000.0, "dims": 32, "scaling": {"factor": 8.0, "fast": 32.0, "original": 2048, "slow": 1.0}}}
+    lat = {"dim": z["dim"], "heads": z["heads"], "kv_rank": z["rank"], "q_rank": 3 * z["rank"] // 2, "rot_dim": z["rot"],
+           "rot": {"base": 10000.0, "dims": z["rot"]}, "scale": (z["dim"] + z["rot"]) ** -0.5, "vdim": z["vdim"]}
+    layers = [{"type": "mingru", "mixer": {"width": W}, "mlp": ff}, {"type": "attention", "mixer": att, "mlp": ff},
+              {"type": "latent_attention", "mixer": lat, "mlp": ff}]
+    return {"architecture": "Dedunex", "layers": layers, "loop": {"start": 1, "stop": 2, "times": 2}, "norm": {"eps": 1e-6, "groups": 8},
+            "vocab": vocab, "width": W}
+
+
+def dedunex_macs_per_token(cfg):
+    """multiply-adds of the projections of one token over all layer runs (attention scores and the scan not counted)"""
+    W, mac = cfg["width"], 0
+    lp = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    for i, ly in enumerate(cfg["layers"]):
+        mx, one = ly["mixer"], 0
+        if ly["type"] == "attention":
+            one = W * (mx["heads"] * 2 * mx["dim"] + mx["kv_heads"] * (2 * mx["dim"] + mx["vdim"])) + mx["heads"] * mx["vdim"] * W
+        elif ly["type"] == "latent_attention":
+            H, d, r, kr, qr, vd = mx["heads"], mx["dim"], mx["rot_dim"], mx["kv_rank"], mx["q_rank"], mx["vdim"]
+            one = W * (qr + kr + r + H) + qr * H * (d + r) + H * d * kr + H * kr * vd + H * vd * W
+        else:
+            one = 4 * W * mx["width"]
+        if ly.get("mlp"):
+            one += 3 * W * ly["mlp"]["ff"]
+        mac += one * (lp["times"] if lp["start"] <= i < lp["stop"] else 1)
+    return mac
+
+
 def run_family_compare(args):
     import numpy as np
     import torch
@@ -565,10 +600,15 @@ def run_family_compare(args):
                                   head_dim=128, vocab=vocab), context=8192)
         pages = (ctx + 64 + 15) // 16 * 9 + (T + 15) // 16 + 8
         rec = {}
-        if args.family == "fosavik":
+        if args.family in ("fosavik", "dedunex"):
             fv = fosavik_config(z, vocab)
             fv_cfg = json.dumps(fv)
             rec["fosavik"] = measure(lambda rows, seqs: q.Engine(config_json=fv_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
+                                                                 max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False)
+        if args.family == "dedunex":
+            dd = dedunex_config(z, vocab)
+            dd_cfg = json.dumps(dd)
+            rec["dedunex"] = measure(lambda rows, seqs: q.Engine(config_json=dd_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
                                                                  max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False)
         if args.family == "ditenex":
             dx = ditenex_config(z, vocab)
@@ -589,7 +629,10 @@ def run_family_compare(args):
         qw_mac = L * (2 * hq * hq + 2 * hq * 2 * 128 + 3 * hq * (z["top"] * z["ff"] + z["sff"]))
         rec["macs_per_token"] = {"nogatar": ng_mac, "qwen": qw_mac}
         fams = [("nogatar", ng_mac), ("qwen_fast", qw_mac)]
-        if args.family == "fosavik":
+        if args.family == "dedunex":
+            rec["macs_per_token"]["dedunex"] = dedunex_macs_per_token(dd)
+            fams.append(("dedunex", rec["macs_per_token"]["dedunex"]))
+        if args.family in ("fosavik", "dedunex"):
             rec["macs_per_token"]["fosavik"] = fosavik_macs_per_token(fv)
             fams.append(("fosavik", rec["macs_per_token"]["fosavik"]))
         if args.family == "ditenex":
@@ -621,8 +664,9 @@ def main():
     ap.add_argument("--family-compare", action="store_true",
                     help="side measurement (not the contract line): prefill / decode throughput of the Nogatar family beside the "
                          "Qwen family at equal size, with per-kernel-class device times")
-    ap.add_argument("--family", default="nogatar", choices=["nogatar", "fosavik", "ditenex"],
-                    help="with --family-compare: which fp32-stream family is measured beside the Qwen family (fosavik and ditenex also run nogatar)")
+    ap.add_argument("--family", default="nogatar", choices=["nogatar", "fosavik", "ditenex", "dedunex"],
+                    help="with --family-compare: which fp32-stream family is measured beside the Qwen family (fosavik and ditenex also run "
+                         "nogatar; dedunex also runs fosavik and nogatar, the families whose mixers are closest to its own)")
     ap.add_argument("--family-size", default="", help="one of " + ", ".join(FAMILY_SIZES) + " (default: all)")
     ap.add_argument("--family-tokens", type=int, default=2048)
     ap.add_argument("--family-ctx", type=int, default=1024)
