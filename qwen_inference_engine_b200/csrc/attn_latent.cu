@@ -116,23 +116,27 @@ __global__ void latent_store_kernel(const LatentCache c, const float* __restrict
   }
 }
 
-// grid (rows, heads)
-__global__ void rope_heads_kernel(const float* __restrict__ src, int ld_src, int hs_src, float* __restrict__ dst, int ld_dst, int hs_dst, int rot,
-                                  const RopeTable rope, const int* __restrict__ pos) {
+// one CTA per row, threads over (head, element)
+__global__ void rope_heads_kernel(const float* __restrict__ src, int ld_src, int hs_src, float* __restrict__ dst, int ld_dst, int hs_dst, int heads,
+                                  int rot, const RopeTable rope, const int* __restrict__ pos) {
   pdl_wait();
   pdl_trigger();
-  const int r = blockIdx.x, h = blockIdx.y, p = pos[r];
-  const float* s = src + (size_t)r * ld_src + (size_t)h * hs_src;
-  float* d = dst + (size_t)r * ld_dst + (size_t)h * hs_dst;
-  const int half = rope.dims / 2;
+  const int r = blockIdx.x, p = pos[r];
+  const int half = rope.dims / 2, rest = rot - rope.dims;
   const int st1 = rope.half_layout ? 1 : 2, off2 = rope.half_layout ? half : 1;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float cs = rope.cos_t[(size_t)p * half + i], sn = rope.sin_t[(size_t)p * half + i];
-    const float u = s[st1 * i], v = s[st1 * i + off2];
-    d[st1 * i] = u * cs - v * sn;
-    d[st1 * i + off2] = v * cs + u * sn;
+  for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;
+    const float* s = src + (size_t)r * ld_src + (size_t)h * hs_src;
+    float* d = dst + (size_t)r * ld_dst + (size_t)h * hs_dst;
+    const float cs = rope.cos_t[(size_t)p * half + j], sn = rope.sin_t[(size_t)p * half + j];
+    const float u = s[st1 * j], v = s[st1 * j + off2];
+    d[st1 * j] = u * cs - v * sn;
+    d[st1 * j + off2] = v * cs + u * sn;
   }
-  for (int i = rope.dims + threadIdx.x; i < rot; i += blockDim.x) d[i] = s[i];
+  for (int i = threadIdx.x; i < heads * rest; i += blockDim.x) {
+    const int h = i / rest, j = rope.dims + (i - h * rest);
+    dst[(size_t)r * ld_dst + (size_t)h * hs_dst + j] = src[(size_t)r * ld_src + (size_t)h * hs_src + j];
+  }
 }
 
 // Shared memory (floats), HP = heads of this CTA rounded up to 8:
@@ -449,6 +453,212 @@ cudaError_t launch_attn_mma(const LatentCache& c, const float* qa, float* out, c
                   block_table, max_pages, hg);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Prompt portions over a bf16 cache, several query rows per CTA.  Consecutive rows of a prompt see almost the same keys,
+// so a CTA takes RT = 8 / WPR consecutive rows and stages every block of TK cached rows ONCE for all of them (double
+// buffered with cp.async).  A warp owns one query row: its 16 heads are the M dimension, S [16 heads, TK keys] = Q K^T stays
+// in registers through mask, online softmax and the re-packing as the A operand of O [16 heads, rank] += P C (the cached
+// row's first `rank` columns, read transposed from the same staged block).  A latent too wide for one warp's registers is
+// split over WPR warps: each computes the row's scores itself and accumulates its own NBO * 8 columns of O.  Rows of
+// another sequence in the same CTA (a batch of short portions) are served in further passes over their own keys.
+// Shared memory: Q bf16 [RT][16][DP] | K blocks bf16 [2][TK][DP] | cache row pointers [2][TK]; DP = D padded so that
+// rows are an odd number of 16-byte pieces apart (ldmatrix without bank conflicts), the padding zero.
+template <int NBO, int TK>
+__global__ void __launch_bounds__(256) latent_attention_rows_kernel(const LatentCache c, const float* __restrict__ qa, float* __restrict__ out,
+                                                                     const bf16* __restrict__ sink, float scale, int window, int H_all,
+                                                                     const int* __restrict__ pos, const int* __restrict__ slot,
+                                                                     const int* __restrict__ block_table, int max_pages, int n, int DP, int WPR,
+                                                                     const HeadGate hg) {
+  extern __shared__ uint4 smq[];
+  __shared__ int s_slot[8], s_pos[8], s_done[8], s_pass[3];  // per row of the CTA; the pass: slot, first key, last key
+  pdl_wait();
+  pdl_trigger();
+  const int D = c.rank + c.rot, R = c.rank, D16 = (D + 15) & ~15, RT = 8 / WPR;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int rl = warp / WPR, part = warp % WPR;  // the warp's row of the CTA and its share of the latent's columns
+  // late rows first: under a causal mask they see the most keys, and the short early rows fill the SMs that finish first
+  const int bx = gridDim.x - 1 - blockIdx.x;
+  const int r = bx * RT + rl;
+  const bool valid = r < n;
+  const int h0 = blockIdx.y * 16, H = min(16, H_all - h0);
+  bf16* s_q = reinterpret_cast<bf16*>(smq);
+  bf16* s_k = s_q + (size_t)RT * 16 * DP;
+  const bf16** krow = reinterpret_cast<const bf16**>(s_k + (size_t)2 * TK * DP);
+  for (int i = tid; i < RT * 16 * DP; i += 256) {
+    const int rr = i / (16 * DP), h = (i / DP) % 16, d = i % DP, row = bx * RT + rr;
+    s_q[i] = f2bf(row < n && h < H && d < D ? qa[((size_t)row * H_all + h0 + h) * D + d] : 0.f);
+  }
+  for (int i = tid; i < 2 * TK * (DP - D); i += 256) s_k[(size_t)(i / (DP - D)) * DP + D + i % (DP - D)] = f2bf(0.f);  // the padding columns
+  if (tid < 8) {
+    const int row = bx * RT + tid;
+    const bool ok = tid < RT && row < n;
+    s_slot[tid] = ok ? slot[row] : -1, s_pos[tid] = ok ? pos[row] : 0, s_done[tid] = ok ? 0 : 1;
+  }
+  const int p = valid ? pos[r] : 0, sl = valid ? slot[r] : -1;
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int chunks = D / 8;
+  while (true) {
+    __syncthreads();
+    if (tid == 0) {  // the next pass: the first unserved row's sequence and the key range of all its rows here
+      int ps = -1, j0 = 0, j1 = 0;
+      for (int i = 0; i < RT; ++i) {
+        if (s_done[i] || (ps >= 0 && s_slot[i] != ps)) continue;
+        const int l = window > 0 ? max(0, s_pos[i] - window + 1) : 0;
+        if (ps < 0) ps = s_slot[i], j0 = l, j1 = s_pos[i];
+        else j0 = min(j0, l), j1 = max(j1, s_pos[i]);
+      }
+      s_pass[0] = ps, s_pass[1] = j0, s_pass[2] = j1;
+    }
+    __syncthreads();
+    const int ps = s_pass[0], jmin = s_pass[1] / TK * TK, jmax = s_pass[2];
+    if (ps < 0) break;
+    const bool active = valid && sl == ps && !s_done[rl];
+    float o[NBO][4];
+#pragma unroll
+    for (int i = 0; i < NBO; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    // running maximum and (per thread partial) sum of the warp's head rows gq and gq + 8; the sink enters as a key without a value
+    const bool sk0 = sink && gq < H, sk1 = sink && gq + 8 < H;
+    float m0 = sk0 ? bf2f(sink[h0 + gq]) : -INFINITY, m1 = sk1 ? bf2f(sink[h0 + gq + 8]) : -INFINITY;
+    float l0 = sk0 && tq == 0 ? 1.f : 0.f, l1 = sk1 && tq == 0 ? 1.f : 0.f;
+    auto stage = [&](int jb, int buf) {
+      if (tid < TK) krow[buf * TK + tid] = jb + tid <= jmax ? cache_row<bf16>(c, block_table, max_pages, ps, jb + tid) : nullptr;
+      __syncthreads();
+      for (int i = tid; i < TK * chunks; i += 256) {
+        const int key = i / chunks, ch = i - key * chunks;
+        bf16* dst = s_k + ((size_t)buf * TK + key) * DP + ch * 8;
+        const bf16* row = krow[buf * TK + key];
+        if (row) cp_async16(smem_u32(dst), row + ch * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      cp_async_commit();
+    };
+    int j0 = jmin, buf = 0;
+    stage(j0, 0);
+    while (true) {
+      const int jn = j0 + TK;
+      const bool more = jn <= jmax;
+      if (more) {
+        stage(jn, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      if (active && j0 <= p && j0 + TK - 1 >= lo) {  // warp-uniform: the block holds keys this row sees
+        const bf16* kt = s_k + (size_t)buf * TK * DP;
+        const bf16* qt = s_q + (size_t)rl * 16 * DP;
+        float s[TK / 8][4];
+#pragma unroll
+        for (int nb = 0; nb < TK / 8; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+        for (int ks = 0; ks < D16; ks += 16) {
+          uint32_t a[4];
+          ldmatrix_x4(a[0], a[1], a[2], a[3], smem_u32(qt + (size_t)(lane & 15) * DP + ks + (lane >> 4) * 8));
+#pragma unroll
+          for (int nb = 0; nb < TK / 8; ++nb) {
+            uint32_t b0, b1;
+            ldmatrix_x2(b0, b1, smem_u32(kt + (size_t)(nb * 8 + (lane & 7)) * DP + ks + ((lane >> 3) & 1) * 8));
+            mma_16816(s[nb], a, b0, b1);
+          }
+        }
+        const bool whole = j0 >= lo && j0 + TK - 1 <= p;  // every key of the block is visible: no mask
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < TK / 8; ++nb)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = j0 + nb * 8 + 2 * tq + (e & 1);
+            s[nb][e] = (whole || (j <= p && j >= lo)) ? s[nb][e] * scale : -INFINITY;
+            if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
+            else mx0 = fmaxf(mx0, s[nb][e]);
+          }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        // the weights become bf16 operands below: the fast exponential's error is far under their rounding
+        const float c0 = m0 > -INFINITY ? __expf(m0 - mn0) : 1.f, c1 = m1 > -INFINITY ? __expf(m1 - mn1) : 1.f;
+        m0 = mn0, m1 = mn1;
+        l0 *= c0, l1 *= c1;
+#pragma unroll
+        for (int i = 0; i < NBO; ++i) o[i][0] *= c0, o[i][1] *= c0, o[i][2] *= c1, o[i][3] *= c1;
+#pragma unroll
+        for (int nb = 0; nb < TK / 8; ++nb) {
+          s[nb][0] = __expf(s[nb][0] - mn0), s[nb][1] = __expf(s[nb][1] - mn0);  // the block has a visible key, so mn is finite
+          s[nb][2] = __expf(s[nb][2] - mn1), s[nb][3] = __expf(s[nb][3] - mn1);
+          l0 += s[nb][0] + s[nb][1];
+          l1 += s[nb][2] + s[nb][3];
+        }
+#pragma unroll
+        for (int kb = 0; kb < TK / 16; ++kb) {
+          uint32_t pa[4];
+          pa[0] = pack2(f2bf(s[2 * kb][0]), f2bf(s[2 * kb][1]));
+          pa[1] = pack2(f2bf(s[2 * kb][2]), f2bf(s[2 * kb][3]));
+          pa[2] = pack2(f2bf(s[2 * kb + 1][0]), f2bf(s[2 * kb + 1][1]));
+          pa[3] = pack2(f2bf(s[2 * kb + 1][2]), f2bf(s[2 * kb + 1][3]));
+#pragma unroll
+          for (int i = 0; i < NBO; ++i) {
+            const int nb = part * NBO + i;
+            if (nb * 8 < R) {  // warp-uniform
+              uint32_t b0, b1;
+              ldmatrix_x2_trans(b0, b1, smem_u32(kt + (size_t)(kb * 16 + (lane & 15)) * DP + nb * 8));
+              mma_16816(o[i], pa, b0, b1);
+            }
+          }
+        }
+      }
+      __syncthreads();  // the stage is free for the block after the next
+      if (!more) break;
+      j0 = jn;
+      buf ^= 1;
+    }
+    if (active) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+      const float f0 = gq < H ? head_gate(hg, r, h0 + gq) / l0 : 0.f, f1 = gq + 8 < H ? head_gate(hg, r, h0 + gq + 8) / l1 : 0.f;
+#pragma unroll
+      for (int i = 0; i < NBO; ++i) {
+        const int d = (part * NBO + i) * 8 + 2 * tq;
+        if (d < R) {
+          if (gq < H) {
+            float* dst = out + ((size_t)r * H_all + h0 + gq) * R + d;
+            dst[0] = o[i][0] * f0, dst[1] = o[i][1] * f0;
+          }
+          if (gq + 8 < H) {
+            float* dst = out + ((size_t)r * H_all + h0 + gq + 8) * R + d;
+            dst[0] = o[i][2] * f1, dst[1] = o[i][3] * f1;
+          }
+        }
+      }
+    }
+    __syncthreads();  // every warp has read s_done of this pass
+    if (active && part == 0 && lane == 0) s_done[rl] = 1;
+  }
+}
+
+// padded row length of the staged blocks: at least 8 more than D (the k-steps of 16 may reach past D), an odd number of 16-byte pieces
+inline int rows_kernel_dp(int D) {
+  int dp = D + 8;
+  if ((dp / 8) % 2 == 0) dp += 8;
+  return dp;
+}
+inline size_t rows_kernel_smem(int D, int RT, int TK) {
+  return ((size_t)RT * 16 + 2 * (size_t)TK) * rows_kernel_dp(D) * sizeof(bf16) + (size_t)2 * TK * sizeof(void*);
+}
+
+template <int NBO, int TK>
+cudaError_t launch_attn_rows(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads, const int* pos,
+                             const int* slot, const int* block_table, int max_pages, int n, int WPR, cudaStream_t st, const HeadGate& hg) {
+  const int D = c.rank + c.rot, RT = 8 / WPR;
+  const size_t smem = rows_kernel_smem(D, RT, TK);
+  cudaError_t r = cudaFuncSetAttribute(latent_attention_rows_kernel<NBO, TK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (r != cudaSuccess) return r;
+  return launch_k(latent_attention_rows_kernel<NBO, TK>, dim3((n + RT - 1) / RT, (heads + 15) / 16), dim3(256), smem, st, c, qa, out, sink, scale, window,
+                  heads, pos, slot, block_table, max_pages, n, rows_kernel_dp(D), WPR, hg);
+}
+
 size_t attn_smem_floats(int H, int D, int R, int TK) {
   const size_t HP = (size_t)((H + 7) & ~7);
   return HP * D + HP * R + (size_t)TK * (D + 1) + (size_t)TK * HP + 3 * HP;
@@ -468,7 +678,7 @@ cudaError_t launch_latent_store(const LatentCache& c, const float* dkv, int ld, 
 cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, float* dst, int ld_dst, int hs_dst, int heads, int rot,
                                   const RopeTable& rope, const int* pos, int n, cudaStream_t st) {
   if (n <= 0 || heads <= 0) return cudaSuccess;
-  return launch_k(rope_heads_kernel, dim3(n, heads), dim3(64), 0, st, src, ld_src, hs_src, dst, ld_dst, hs_dst, rot, rope, pos);
+  return launch_k(rope_heads_kernel, dim3(n), dim3(128), 0, st, src, ld_src, hs_src, dst, ld_dst, hs_dst, heads, rot, rope, pos);
 }
 
 cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads,
@@ -480,6 +690,22 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
   static const bool mma_on = [] { const char* v = getenv("QIE_ATTN_MMA"); return !(v && v[0] == '0'); }();
   if (mma_on && c.elt_bytes == 2 && n >= 64 && c.rank % 8 == 0 && c.rot % 8 == 0 && c.rank <= 512 && c.page_elems % 8 == 0 &&
       c.layer_off % 8 == 0 && (reinterpret_cast<uintptr_t>(c.pool) & 15) == 0) {
+    // several rows per CTA over shared key blocks (QIE_LATENT_ROWS=0 keeps the one-row kernel for A/B): the fewest warps per
+    // row whose accumulators hold the latent (32 blocks of 8 columns each at most) and whose shared memory fits
+    static const bool rows_on = [] { const char* v = getenv("QIE_LATENT_ROWS"); return !(v && v[0] == '0'); }();
+    if (rows_on) {
+      const int nb = (c.rank + 7) / 8;
+      for (int tk : {64, 32}) {
+        int wpr = 1;
+        while (wpr < 8 && (nb > 32 * wpr || rows_kernel_smem(D, 8 / wpr, tk) > 200 * 1024)) wpr *= 2;
+        if (nb > 32 * wpr || rows_kernel_smem(D, 8 / wpr, tk) > 200 * 1024 || (tk == 64 && wpr > 2)) continue;
+        const int nbo = (nb + wpr - 1) / wpr;
+#define ROWS_GO(NBO, TK) launch_attn_rows<NBO, TK>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, wpr, st, hg)
+        if (tk == 64) return nbo <= 4 ? ROWS_GO(4, 64) : nbo <= 8 ? ROWS_GO(8, 64) : nbo <= 16 ? ROWS_GO(16, 64) : ROWS_GO(32, 64);
+        return nbo <= 8 ? ROWS_GO(8, 32) : nbo <= 16 ? ROWS_GO(16, 32) : ROWS_GO(32, 32);
+#undef ROWS_GO
+      }
+    }
     cudaError_t r = cudaErrorInvalidConfiguration;
     if (c.rank <= 64) r = launch_attn_mma<1>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st, hg);
     else if (c.rank <= 128) r = launch_attn_mma<2>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st, hg);
