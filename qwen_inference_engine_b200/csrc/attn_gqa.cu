@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
           v1 = (rv1 ? out1[c + e] : 0.f) - a.lam * v1;
           sq0 = fmaf(v0, v0, sq0), sq1 = fmaf(v1, v1, sq1);
           o[vb][e] = v0, o[vb][2 + e] = v1;
-        } else if (a.out_bf) {
+        } else if (a.out_bf && last) {  // (the first of two maps waits in the fp32 rows)
           if (rv0) a.out_bf[(size_t)(row0 + wrow + qr) * a.ldo_bf + (size_t)h * vd + c + e] = f2bf(v0);
           if (rv1) a.out_bf[(size_t)(row0 + wrow + qr + 8) * a.ldo_bf + (size_t)h * vd + c + e] = f2bf(v1);
         } else {
@@ -546,6 +546,11 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           if (c + e >= vd) continue;
+          if (a.out_bf) {
+            if (rv0) a.out_bf[(size_t)(row0 + wrow + qr) * a.ldo_bf + (size_t)h * vd + c + e] = f2bf(o[vb][e] * r0);
+            if (rv1) a.out_bf[(size_t)(row0 + wrow + qr + 8) * a.ldo_bf + (size_t)h * vd + c + e] = f2bf(o[vb][2 + e] * r1);
+            continue;
+          }
           if (rv0) out0[c + e] = o[vb][e] * r0;
           if (rv1) out1[c + e] = o[vb][2 + e] * r1;
         }
@@ -657,7 +662,7 @@ cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_l
   if (a.n <= 0) return cudaSuccess;
   if (a.shared_keys && (a.maps != 1 || a.dim != a.c.kw)) return cudaErrorInvalidValue;
   if (a.finish == 3 && !a.gate) return cudaErrorInvalidValue;
-  if (a.out_bf && a.maps != 1) return cudaErrorInvalidValue;
+  if (a.out_bf && a.maps != 1 && !a.out) return cudaErrorInvalidValue;  // two maps: the first one's result waits in the fp32 rows
   // prompt portions over a bf16 cache: the tensor-core kernel (one launch, no workspace); QIE_ATTN_MMA=0 keeps the per-row kernel (A/B)
   static const bool mma_on = [] { const char* v = getenv("QIE_ATTN_MMA"); return !(v && v[0] == '0'); }();
   if (mma_on && a.seg_start && a.c.elt_bytes == 2 && a.n >= 64 && a.dim <= 128 && a.vdim <= 128 && a.maps <= 2 && a.heads % a.kv_heads == 0 &&

@@ -469,10 +469,12 @@ cudaError_t DdModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       g.pos = e->pos_d, g.slot = e->slot_d, g.block_table = e->block_table_d, g.max_pages = e->max_pages_per_seq, g.n = n, g.max_keys = max_kv_len;
       g.ws = m->attn_ws, g.ws_floats = m->attn_ws_floats, g.num_sms = e->num_sms;
       g.seg_start = segs, g.seg_slot = seg_sl, g.n_seg = n_seg;
+      const bool tc_o = tcfit(H * vd, W, L.wo);
+      if (tc_o) g.out_bf = m->mb, g.ldo_bf = H * vd;  // bf16 rows for the output projection (the fp32 rows hold the first map meanwhile)
       int nl = 0;
       FAM_TRY(KK_GQA_ATTN, launch_gqa_attention(g, st, &nl));
       e->launches += nl > 0 ? nl - 1 : 0;
-      Km = H * vd, mix_f = m->p1;
+      Km = H * vd, mix_f = tc_o ? nullptr : m->p1;
     } else if (L.type == 1) {
       const int H = L.heads, d = L.dim, vd = L.vdim, r = L.rot_dim, kr = L.kv_rank, D = kr + r, Nq = H * (d + r), qk = L.q_rank;
       LatentCache c;

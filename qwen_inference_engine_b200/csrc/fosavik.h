@@ -123,7 +123,7 @@ struct GqaAttnArgs {
   int ldq = 0;
   float* out = nullptr;
   int ldo = 0;
-  bf16* out_bf = nullptr;  // maps == 1: the result goes here as bf16 rows (row stride ldo_bf) instead of `out`
+  bf16* out_bf = nullptr;  // the result goes here as bf16 rows (row stride ldo_bf) instead of `out` (two maps: `out` is still needed as scratch)
   int ldo_bf = 0;
   int heads = 0, kv_heads = 0, dim = 0, vdim = 0, maps = 1;
   float scale = 1.f, softcap = 0.f;

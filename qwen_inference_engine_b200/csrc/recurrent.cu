@@ -302,16 +302,26 @@ __global__ void __launch_bounds__(64) mingru_chunk_carry_kernel(const MinGruArgs
   float* sums = a.ws + 2 * (size_t)a.n_rows * C;
   float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + c;
   float S = *sp;
-  for (int k = 0; r0 + k * MG_CHUNK < r1; ++k) {
-    float* w = sums + (size_t)mg_chunk_id(r0, seg, k) * 2 * C;
-    const float P = w[c], Q = w[C + c];
-    w[c] = S;  // the chunk's incoming state
-    S = fmaf(P, S, Q);
+  const int nk = (r1 - r0 + MG_CHUNK - 1) / MG_CHUNK;
+  for (int k0 = 0; k0 < nk; k0 += 8) {  // the summaries of eight chunks are loaded together; the chain itself is one FMA per chunk
+    float P[8], Q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float* w = sums + (size_t)mg_chunk_id(r0, seg, min(k0 + j, nk - 1)) * 2 * C;
+      P[j] = w[c], Q[j] = w[C + c];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (k0 + j < nk) {
+        sums[(size_t)mg_chunk_id(r0, seg, k0 + j) * 2 * C + c] = S;  // the chunk's incoming state
+        S = fmaf(P[j], S, Q[j]);
+      }
   }
   *sp = S;
 }
 
-__global__ void __launch_bounds__(128) mingru_chunk_apply_kernel(const MinGruArgs a) {
+// block (128 channels, 4 row lanes): the apply pass is elementwise over a chunk's rows
+__global__ void __launch_bounds__(512) mingru_chunk_apply_kernel(const MinGruArgs a) {
   pdl_wait();
   pdl_trigger();
   const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x, k = blockIdx.z;
@@ -322,7 +332,7 @@ __global__ void __launch_bounds__(128) mingru_chunk_apply_kernel(const MinGruArg
   const float* local = a.ws;
   const float* cumw = a.ws + (size_t)a.n_rows * C;
   const float Sin = cumw[(size_t)a.n_rows * C + (size_t)mg_chunk_id(r0, seg, k) * 2 * C + c];
-  for (int t = t0; t < t1; ++t) {
+  for (int t = t0 + threadIdx.y; t < t1; t += blockDim.y) {
     const float S = fmaf(cumw[(size_t)t * C + c], Sin, local[(size_t)t * C + c]);
     mg_store(a, (size_t)t, c, S, mg_ld(a.gp, a.gp_bf, (size_t)t * ld + c));
   }
@@ -530,7 +540,7 @@ cudaError_t launch_mingru_scan(const MinGruArgs& a, cudaStream_t st) {
     cudaError_t r = launch_k(mingru_chunk_local_kernel, dim3(a.n_seg, (a.channels + 63) / 64, chunks), dim3(64), 0, st, a);
     if (r != cudaSuccess) return r;
     if ((r = launch_k(mingru_chunk_carry_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a)) != cudaSuccess) return r;
-    return launch_k(mingru_chunk_apply_kernel, dim3(a.n_seg, (a.channels + 127) / 128, chunks), dim3(128), 0, st, a);
+    return launch_k(mingru_chunk_apply_kernel, dim3(a.n_seg, (a.channels + 127) / 128, chunks), dim3(128, 4), 0, st, a);
   }
   return launch_k(mingru_scan_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a);
 }
