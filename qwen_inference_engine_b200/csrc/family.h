@@ -1,7 +1,7 @@
-// family.h -- what the model families with a general row forward share (Nogatar, Fosavik): the interface the engine
+// family.h -- what the model families with a general row forward share (Nogatar, Fosavik, Ditenex, Dedunex): the interface the engine
 // drives them through (forward over rows, slot reset, release), the weight blob helpers (tensor layout, safetensors
-// reader, synthetic fill) and the projection helper that puts a plain GEMM on the tcgen05 kernel when precision and
-// shape allow.  A row is (sequence slot, position); rows of one sequence are consecutive and in position order
+// reader, synthetic fill), the rotary tables and the projection helper that puts a plain GEMM on the tcgen05 kernel when
+// precision and shape allow.  A row is (sequence slot, position); rows of one sequence are consecutive and in position order
 // (a "segment"); rows of different sequences may be portions of prompts next to single decoded tokens.
 #pragma once
 #include <cuda_runtime.h>
