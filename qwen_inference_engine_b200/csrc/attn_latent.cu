@@ -7,9 +7,12 @@
 // (one extra term exp(sink_h) in the denominator that carries no value).
 //
 // One CTA per query row: the row's key window is streamed through shared memory in tiles that all heads share;
-// scores, the running maximum / sum and the latent accumulator are fp32.  Keys are always read from the cache
-// (the row's own position was stored by launch_latent_store before), so the result does not depend on how a
-// prompt was cut into forwards or on the other rows of the launch.
+// scores, the running maximum / sum and the latent accumulator are fp32.  Prompt portions over a bf16 cache run on
+// tensor cores, eight query rows per CTA over key blocks staged once (latent_attention_rows_kernel below).  Options of
+// the store and the attention: the pairing of the rotated dimensions, a second normed vector per row (a query latent),
+// a sigmoid gate per (row, head) on the result.  Keys are always read from the cache (the row's own position was
+// stored by launch_latent_store before), so the result does not depend on how a prompt was cut into forwards or on
+// the other rows of the launch.
 #include <stdlib.h>
 
 #include <algorithm>
