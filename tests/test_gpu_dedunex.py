@@ -327,6 +327,28 @@ def test_greedy_generation_through_engine_and_scheduler(tmp_path):
         eng.close()
 
 
+def test_top_k_sampling_draws_from_the_best_tokens(tmp_path):
+    # the engine's sampler on this family's logits: with top-k 3 every drawn token is among the three largest logits of
+    # its position (the oracle's, where the third and fourth are clearly apart), and top-k 1 is the greedy choice
+    cfg = U.make_config(_mixed_layers()[:3], width=24, vocab=61, groups=4, loop=(1, 3, 2))
+    w = U.random_weights(cfg, seed=41, gain=1.5)
+    prompt = _tokens(cfg, 11, 3)
+    eng = _engine(tmp_path, cfg, w, page_size=8, max_pages=12, max_seqs=2, rows=64)
+    greedy = eng.generate(prompt, 6)
+    eng.set_sampling(topk=1)
+    assert eng.generate(prompt, 6) == greedy
+    eng.set_sampling(topk=3, temperature_prefill=1.0, temperature_decode=1.0, seed=7)
+    drawn = eng.generate(prompt, 8)
+    eng.close()
+    st = O.Stepper(cfg, U.values(w))
+    z = st.run(prompt)[0][-1]
+    for t in drawn:
+        order = np.argsort(z)[::-1]
+        if z[order[2]] - z[order[3]] > 1e-3:
+            assert t in order[:3]
+        z = st.run([t])[0][-1]
+
+
 def _row_err(got, want):
     return np.sqrt(((got - want) ** 2).mean(-1)) / np.sqrt((want ** 2).mean(-1))
 
