@@ -402,3 +402,23 @@ def test_bf16_other_sizes(tmp_path):
     for got in (whole, cut):
         err = _row_err(got, right)
         assert np.median(err) < 1e-2 and np.quantile(err, 0.95) < 3e-2, (np.median(err), err.max())
+
+
+@pytest.mark.parametrize("heads,kv_rank,rot_dim", [(20, 40, 8), (3, 264, 16), (2, 8, 0)], ids=["two_head_groups", "latent_over_two_warps", "tiny_no_rotation"])
+def test_bf16_latent_prompt_kernel_shapes(tmp_path, heads, kv_rank, rot_dim):
+    # the tensor-core latent attention of prompt portions takes eight rows per CTA: more than 16 heads (two head groups), a latent
+    # too wide for one warp's accumulators, rows of three sequences in one batch (a CTA then holds rows of two sequences and
+    # serves them in passes), a portion that continues a cached prefix
+    cfg = U.make_config([U.latent(heads=heads, dim=8, vdim=8, rot_dim=rot_dim, kv_rank=kv_rank, q_rank=24, scale=0.4)], width=32, vocab=29, groups=2)
+    w = U.random_weights(cfg, seed=43, gain=1.5)
+    reqs = [_tokens(cfg, n, 50 + i) for i, n in enumerate([83, 5, 97])]
+    right = [_oracle_logits(cfg, w, t) for t in reqs]
+    eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=24, rows=256)
+    seqs = [eng.new_sequence() for _ in reqs]
+    lg = eng.forward_batch([(seqs[0], reqs[0][:70]), (seqs[1], reqs[1]), (seqs[2], reqs[2][:20])], range(95))
+    lg2 = eng.forward_batch([(seqs[2], reqs[2][20:]), (seqs[0], reqs[0][70:])], range(90))
+    eng.close()
+    got = [np.concatenate([lg[:70], lg2[77:]]), lg[70:75], np.concatenate([lg[75:], lg2[:77]])]
+    for g, r in zip(got, right):
+        err = _row_err(g, r)
+        assert np.median(err) < 1e-2 and err.max() < 4e-2, (np.median(err), err.max())
